@@ -436,3 +436,130 @@ MS_EXPORT int ms_latent_prepare(void* pool, const void* proj, int ld, int off, c
               off, w, eps, positions, row_of_token, page_indptr, page_indices, num_tokens, rank, d_pad, page_shift, num_pages, status);
   return 0;
 }
+
+// ---------------------------------------------------------------- latent attention with a rotated part
+//   * a column range of a projection divided by its root mean square, times a float32 weight (the queries' latent);
+//   * what is cached per token when the keys have a rotated part shared by all heads beside the latent:
+//     [latent (RMS-normed, times its weight) | rotated part, turned by the token's position | zeros], and the queries'
+//     rotated parts turned likewise and written behind the latent-sized part of every query head.
+namespace ms {
+
+// One warp per row: out[t, 0:n] = x[t, 0:n] / sqrt(mean x^2 + eps) * w.
+template <typename T>
+__global__ void row_rmsnorm_kernel(T* __restrict__ out, int ld_out, const T* __restrict__ x, int ld_x, const float* __restrict__ w,
+                                   int rows, int n, float eps) {
+  pdl_prologue();
+  const int lane = threadIdx.x & 31;
+  const int t = blockIdx.x * (blockDim.x >> 5) + (threadIdx.x >> 5);
+  if (t >= rows) return;
+  const T* src = x + (size_t)t * ld_x;
+  float ss = 0.f;
+  for (int c = lane; c < n; c += 32) {
+    const float v = Elem<T>::load(src + c);
+    ss += v * v;
+  }
+  ss = warp_sum(ss);
+  const float inv = 1.0f / sqrtf(ss / (float)n + eps);
+  for (int c = lane; c < n; c += 32) Elem<T>::store(out + (size_t)t * ld_out + c, (Elem<T>::load(src + c) * inv) * w[c]);
+}
+
+// One warp per (token, unit). Unit 0: the token's cache entry. Units 1..H: query head unit - 1, whose rotated part
+// q[t, h, q_dim : q_dim + rot] goes to qp[t, h, rank : rank + rot] (zeros from there to d_pad). cos_sin [T, rot]: cosines
+// of the rot / 2 pairs, then sines (any factor on both already applied); pair i is (i, i + rot / 2).
+template <typename T>
+__global__ void latent_rope_prepare_kernel(T* __restrict__ pool,  // [pages, 1, page_size, d_pad]
+                                           const T* __restrict__ kv, int ld_kv, const float* __restrict__ w, float eps,
+                                           const T* __restrict__ q, int ld_q, int H, int q_dim, T* __restrict__ qp,
+                                           const float* __restrict__ cos_sin, const int* __restrict__ positions,
+                                           const int* __restrict__ row_of_token, const int* __restrict__ page_indptr,
+                                           const int* __restrict__ page_indices, int num_tokens, int rank, int rot, int d_pad,
+                                           int page_shift, int num_pages, int* __restrict__ status) {
+  pdl_prologue();
+  const int lane = threadIdx.x & 31;
+  const long long item = (long long)blockIdx.x * (blockDim.x >> 5) + (threadIdx.x >> 5);
+  if (item >= (long long)num_tokens * (H + 1)) return;
+  const int t = (int)(item / (H + 1)), unit = (int)(item - (long long)t * (H + 1));
+  const int half = rot >> 1;
+  const float* cs = cos_sin + (size_t)t * rot;
+  if (unit > 0) {
+    const int h = unit - 1;
+    const T* src = q + (size_t)t * ld_q + (size_t)h * (q_dim + rot) + q_dim;
+    T* dst = qp + ((size_t)t * H + h) * d_pad + rank;
+    for (int i = lane; i < half; i += 32) {
+      const float u = Elem<T>::load(src + i), v = Elem<T>::load(src + half + i);
+      const float c = cs[i], s = cs[half + i];
+      Elem<T>::store(dst + i, u * c - v * s);
+      Elem<T>::store(dst + half + i, v * c + u * s);
+    }
+    for (int i = rot + lane; i < d_pad - rank; i += 32) Elem<T>::store(dst + i, 0.f);
+    return;
+  }
+  const T* src = kv + (size_t)t * ld_kv;
+  const int pos = positions[t], row = row_of_token[t];
+  const int page_size = 1 << page_shift;
+  const int page = page_indices[page_indptr[row] + (pos >> page_shift)];
+  if (page < 0) {
+    if (lane == 0) atomicExch(status, 2);
+    return;
+  }
+  MS_DEBUG_ONLY(if (page >= num_pages || row < 0) {
+    if (lane == 0) atomicExch(status, 5);
+    return;
+  })
+  T* dst = pool + ((size_t)page * page_size + (pos & (page_size - 1))) * d_pad;
+  float ss = 0.f;
+  for (int c = lane; c < rank; c += 32) {
+    const float x = Elem<T>::load(src + c);
+    ss += x * x;
+  }
+  ss = warp_sum(ss);
+  const float inv = 1.0f / sqrtf(ss / (float)rank + eps);
+  for (int c = lane; c < rank; c += 32) Elem<T>::store(dst + c, (Elem<T>::load(src + c) * inv) * w[c]);
+  for (int i = lane; i < half; i += 32) {
+    const float u = Elem<T>::load(src + rank + i), v = Elem<T>::load(src + rank + half + i);
+    const float c = cs[i], s = cs[half + i];
+    Elem<T>::store(dst + rank + i, u * c - v * s);
+    Elem<T>::store(dst + rank + half + i, v * c + u * s);
+  }
+  for (int c = rank + rot + lane; c < d_pad; c += 32) Elem<T>::store(dst + c, 0.f);
+}
+
+}  // namespace ms
+
+MS_EXPORT int ms_row_rmsnorm(void* out, int ld_out, const void* x, int ld_x, const float* w, int rows, int n, float eps, int dtype,
+                             cudaStream_t stream) {
+  if (rows == 0) return 0;
+  MS_CHECK_ARG(n > 0, "row_rmsnorm: %d columns", n);
+  const int warps = 4;
+  const unsigned blocks = (unsigned)((rows + warps - 1) / warps);
+  if (dtype == MS_F32)
+    MS_LAUNCH(row_rmsnorm_kernel<float>, blocks, warps * 32, 0, stream, (float*)out, ld_out, (const float*)x, ld_x, w, rows, n, eps);
+  else
+    MS_LAUNCH(row_rmsnorm_kernel<__nv_bfloat16>, blocks, warps * 32, 0, stream, (__nv_bfloat16*)out, ld_out, (const __nv_bfloat16*)x,
+              ld_x, w, rows, n, eps);
+  return 0;
+}
+
+MS_EXPORT int ms_latent_rope_prepare(void* pool, const void* kv, int ld_kv, const float* w, float eps, const void* q, int ld_q, int H,
+                                     int q_dim, void* qp, const float* cos_sin, const int* positions, const int* row_of_token,
+                                     const int* page_indptr, const int* page_indices, int num_tokens, int rank, int rot, int d_pad,
+                                     int page_size, int num_pages, int* status, int dtype, cudaStream_t stream) {
+  if (num_tokens == 0) return 0;
+  MS_CHECK_ARG(rank > 0 && rot > 0 && rot % 2 == 0 && d_pad >= rank + rot, "latent_rope_prepare: bad sizes rank=%d rot=%d D=%d", rank, rot,
+               d_pad);
+  MS_CHECK_ARG(page_size > 0 && (page_size & (page_size - 1)) == 0, "latent_rope_prepare: page_size=%d must be a power of two", page_size);
+  int page_shift = 0;
+  while ((1 << page_shift) < page_size) ++page_shift;
+  const int warps = 4;
+  const long long items = (long long)num_tokens * (H + 1);
+  const unsigned blocks = (unsigned)((items + warps - 1) / warps);
+  if (dtype == MS_F32)
+    MS_LAUNCH(latent_rope_prepare_kernel<float>, blocks, warps * 32, 0, stream, (float*)pool, (const float*)kv, ld_kv, w, eps,
+              (const float*)q, ld_q, H, q_dim, (float*)qp, cos_sin, positions, row_of_token, page_indptr, page_indices, num_tokens, rank,
+              rot, d_pad, page_shift, num_pages, status);
+  else
+    MS_LAUNCH(latent_rope_prepare_kernel<__nv_bfloat16>, blocks, warps * 32, 0, stream, (__nv_bfloat16*)pool, (const __nv_bfloat16*)kv,
+              ld_kv, w, eps, (const __nv_bfloat16*)q, ld_q, H, q_dim, (__nv_bfloat16*)qp, cos_sin, positions, row_of_token, page_indptr,
+              page_indices, num_tokens, rank, rot, d_pad, page_shift, num_pages, status);
+  return 0;
+}

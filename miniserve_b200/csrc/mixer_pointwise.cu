@@ -413,3 +413,28 @@ MS_EXPORT int ms_qkv_prepare(void* q_out, void* k_pool, void* v_pool, const void
               num_pages, status);
   return 0;
 }
+
+// out[t, c] = act(gate_up[t, c]) * gate_up[t, inter + c]: a gated feed-forward's inner step for a stacked gate|up
+// product; act 0: SiLU, 1: the tanh form of GELU. float32 arithmetic, one rounding.
+namespace ms {
+template <typename T>
+__global__ void act_mul_kernel(T* __restrict__ out, const T* __restrict__ gate_up, int inter, long long total, int act) {
+  pdl_prologue();
+  const long long idx = (long long)blockIdx.x * blockDim.x + threadIdx.x;
+  if (idx >= total) return;
+  const long long t = idx / inter;
+  const int c = (int)(idx - t * inter);
+  const float g = Elem<T>::load(gate_up + t * 2 * inter + c), u = Elem<T>::load(gate_up + t * 2 * inter + inter + c);
+  const float a = act == 0 ? g / (1.0f + expf(-g)) : 0.5f * g * (1.0f + tanhf(0.7978845608028654f * (g + 0.044715f * g * g * g)));
+  Elem<T>::store(out + idx, a * u);
+}
+}  // namespace ms
+
+MS_EXPORT int ms_act_mul(void* out, const void* gate_up, int tokens, int inter, int act, int dtype, cudaStream_t stream) {
+  if (tokens == 0 || inter == 0) return 0;
+  const long long total = (long long)tokens * inter;
+  const unsigned blocks = (unsigned)((total + 255) / 256);
+  if (dtype == MS_F32) MS_LAUNCH(act_mul_kernel<float>, blocks, 256, 0, stream, (float*)out, (const float*)gate_up, inter, total, act);
+  else MS_LAUNCH(act_mul_kernel<__nv_bfloat16>, blocks, 256, 0, stream, (__nv_bfloat16*)out, (const __nv_bfloat16*)gate_up, inter, total, act);
+  return 0;
+}

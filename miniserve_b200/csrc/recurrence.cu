@@ -72,7 +72,7 @@ decay_scan_kernel(float* __restrict__ o_out,   // [T, H, dv]
                   const TZ* __restrict__ z, int ld_z, const float* __restrict__ z_bias, const float* __restrict__ decay_coef,
                   float z_sign, int z_is_decay, const TZ* __restrict__ beta, int ld_beta,
                   const int* __restrict__ cu_q, const int* __restrict__ q_start, const int* __restrict__ state_slot,
-                  int H, int dk, int dv, int L, int chunk, float q_scale, int vec) {
+                  int H, int dk, int dv, int L, int chunk, float q_scale, int vec, int dkz, const float* __restrict__ v_scale) {
   // words a thread's channels take in shared memory: padded so that the 16-byte loads of a quarter warp's lanes fall on different banks
   constexpr int SCAN_SEG = SCAN_KPT == 4 ? 4 : SCAN_KPT + 4;
   extern __shared__ __align__(16) float smem[];
@@ -117,12 +117,19 @@ decay_scan_kernel(float* __restrict__ o_out,   // [T, H, dv]
         float fq[8], fk[8], fz[8];
         load8(q + tok * ld_q + (size_t)qk_head * dk + i, fq);
         load8(k + tok * ld_k + (size_t)qk_head * dk + i, fk);
-        load8(z + tok * ld_z + (size_t)h * dk + i, fz);
+        if (dkz == 1) {  // one decay for all key channels of the head
+          float zz = Elem<TZ>::load(z + tok * ld_z + h);
+          if (!z_is_decay) zz = decay_of(zz + z_bias[h], coef, z_sign);
+#pragma unroll
+          for (int e = 0; e < 8; ++e) fz[e] = zz;
+        } else {
+          load8(z + tok * ld_z + (size_t)h * dk + i, fz);
+        }
         const int at = tt * dkp + (i / SCAN_KPT) * SCAN_SEG + (i % SCAN_KPT);
 #pragma unroll
         for (int e = 0; e < 8; ++e) {
           fq[e] *= q_scale;
-          if (!z_is_decay) fz[e] = decay_of(fz[e] + z_bias[(size_t)h * dk + i + e], coef, z_sign);
+          if (!z_is_decay && dkz != 1) fz[e] = decay_of(fz[e] + z_bias[(size_t)h * dk + i + e], coef, z_sign);
         }
 #pragma unroll
         for (int e = 0; e < 8; e += 4) {
@@ -138,14 +145,17 @@ decay_scan_kernel(float* __restrict__ o_out,   // [T, H, dv]
       const int at = tt * dkp + (i / SCAN_KPT) * SCAN_SEG + (i % SCAN_KPT);
       qs[at] = Elem<TIn>::load(q + tok * ld_q + (size_t)qk_head * dk + i) * q_scale;
       ks[at] = Elem<TIn>::load(k + tok * ld_k + (size_t)qk_head * dk + i);
-      const float zz = Elem<TZ>::load(z + tok * ld_z + (size_t)h * dk + i);
-      ds[at] = z_is_decay ? zz : decay_of(zz + z_bias[(size_t)h * dk + i], coef, z_sign);
+      const size_t zc = dkz == 1 ? (size_t)h : (size_t)h * dk + i;
+      const float zz = Elem<TZ>::load(z + tok * ld_z + zc);
+      ds[at] = z_is_decay ? zz : decay_of(zz + z_bias[zc], coef, z_sign);
     }
 #pragma unroll 8
     for (int idx = tid; idx < n * cols; idx += threads) {
       const int tt = idx / cols, c = idx - tt * cols;
       const int jj = blockIdx.z * cols + c;
-      vs[idx] = jj < dv ? Elem<TIn>::load(v + (size_t)(c0 + tt) * ld_v + (size_t)h * dv + jj) : 0.f;
+      float vv = jj < dv ? Elem<TIn>::load(v + (size_t)(c0 + tt) * ld_v + (size_t)h * dv + jj) : 0.f;
+      if (v_scale) vv *= v_scale[(size_t)(c0 + tt) * H + h];
+      vs[idx] = vv;
     }
     if (DELTA) {
       for (int tt = tid; tt < n; tt += threads)
@@ -256,7 +266,7 @@ __global__ void segment_cumprod_kernel(float* __restrict__ c, const float* __res
 __global__ void segment_combine_kernel(float* __restrict__ state, const float* __restrict__ ends, float* __restrict__ before,
                                        const float* __restrict__ c, const int* __restrict__ seg_cu,
                                        const int* __restrict__ q_start, const int* __restrict__ state_slot, int num_rows, int P,
-                                       int H, int dk, int dv) {
+                                       int H, int dk, int dv, int dkz) {
   pdl_prologue();
   const long long per_row = (long long)H * dv * dk;
   const long long idx = (long long)blockIdx.x * blockDim.x + threadIdx.x;
@@ -270,7 +280,7 @@ __global__ void segment_combine_kernel(float* __restrict__ state, const float* _
     const int sg = r * P + sgm;
     before[(size_t)sg * per_row + e] = S;
     const int first = seg_cu[sg], end = seg_cu[sg + 1];
-    if (end > first) S = c[(size_t)(end - 1) * H * dk + (size_t)h * dk + i] * S + ends[(size_t)sg * per_row + e];
+    if (end > first) S = c[(size_t)(end - 1) * H * dkz + (size_t)h * dkz + (dkz == 1 ? 0 : i)] * S + ends[(size_t)sg * per_row + e];
   }
   *slot = S;
 }
@@ -283,7 +293,7 @@ template <typename TIn>
 __global__ void __launch_bounds__(FIX_THREADS)
 segment_fixup_kernel(float* __restrict__ o, const TIn* __restrict__ q, int ld_q, int qk_group, const float* __restrict__ c,
                      const float* __restrict__ before, const int* __restrict__ seg_cu, const int* __restrict__ q_start, int P,
-                     int H, int dk, int dv, int cols, float q_scale) {
+                     int H, int dk, int dv, int cols, float q_scale, int dkz) {
   extern __shared__ float fix_smem[];
   pdl_prologue();
   const int sg = blockIdx.x, h = blockIdx.y;
@@ -297,7 +307,7 @@ segment_fixup_kernel(float* __restrict__ o, const TIn* __restrict__ q, int ld_q,
   for (int idx = threadIdx.x; idx < n * dk; idx += FIX_THREADS) {
     const int tt = idx / dk, i = idx - tt * dk;
     const size_t tok = (size_t)(t0 + tt);
-    qc[idx] = Elem<TIn>::load(q + tok * ld_q + (size_t)qk_head * dk + i) * q_scale * c[tok * H * dk + (size_t)h * dk + i];
+    qc[idx] = Elem<TIn>::load(q + tok * ld_q + (size_t)qk_head * dk + i) * q_scale * c[tok * H * dkz + (size_t)h * dkz + (dkz == 1 ? 0 : i)];
   }
   for (int j0 = 0; j0 < dv; j0 += cols) {
     const int ncols = min(cols, dv - j0);
@@ -333,7 +343,7 @@ __global__ void conv_silu_unit_kernel(float* __restrict__ out, const T* __restri
                                       const float* __restrict__ w, const int* __restrict__ row_of_token,
                                       const int* __restrict__ cu_q, const int* __restrict__ q_start,
                                       const int* __restrict__ state_slot, int num_tokens, int C, int taps, int unit_heads,
-                                      int dk, int other_heads, int dv, float unit_eps) {
+                                      int dk, int other_heads, int dv, float unit_eps, const float* __restrict__ bias) {
   pdl_prologue();
   const int lane = threadIdx.x & 31;
   const int units = unit_heads + other_heads;
@@ -350,7 +360,7 @@ __global__ void conv_silu_unit_kernel(float* __restrict__ out, const T* __restri
   float ss = 0.f;
   for (int c = lane; c < size; c += 32) {
     const int ch = base + c;
-    float acc = 0.f;
+    float acc = bias ? bias[ch] : 0.f;
     for (int jt = 0; jt < taps; ++jt) {
       const int back = taps - 1 - jt;
       const int at = local - back;
@@ -420,7 +430,7 @@ template <typename TIn, typename TZ, bool DELTA, int SCAN_KPT>
 int launch_scan_kpt(float* o_out, float* state, const void* q, int ld_q, const void* k, int ld_k, int qk_group, const void* v, int ld_v,
                 const void* z, int ld_z, const float* z_bias, const float* decay_coef, float z_sign, int z_is_decay, const void* beta,
                 int ld_beta, const int* cu_q, const int* q_start, const int* state_slot, int num_rows, int H, int dk, int dv, float q_scale,
-                cudaStream_t stream) {
+                int dkz, const float* v_scale, cudaStream_t stream) {
   constexpr int SCAN_SEG = SCAN_KPT == 4 ? 4 : SCAN_KPT + 4;
   int L = 1;
   while (L * SCAN_KPT < dk) L <<= 1;
@@ -443,11 +453,11 @@ int launch_scan_kpt(float* o_out, float* state, const void* q, int ld_q, const v
   const dim3 grid(num_rows, H, (dv + cols - 1) / cols);
   // 16-byte loads while staging: every row of q, k and z starts on 16 bytes and heads are whole groups of eight
   const int in8 = 16 / (int)sizeof(TIn), z8 = 16 / (int)sizeof(TZ);
-  const int vec = dk % 8 == 0 && (uintptr_t)q % 16 == 0 && (uintptr_t)k % 16 == 0 && (uintptr_t)z % 16 == 0 && ld_q % in8 == 0 &&
-                  ld_k % in8 == 0 && ld_z % z8 == 0;
+  const int vec = dk % 8 == 0 && (uintptr_t)q % 16 == 0 && (uintptr_t)k % 16 == 0 && ld_q % in8 == 0 && ld_k % in8 == 0 &&
+                  (dkz == 1 || ((uintptr_t)z % 16 == 0 && ld_z % z8 == 0));
   MS_LAUNCH(kernel, grid, threads, smem, stream, o_out, state, (const TIn*)q, ld_q, (const TIn*)k, ld_k, qk_group,
             (const TIn*)v, ld_v, (const TZ*)z, ld_z, z_bias, decay_coef, z_sign, z_is_decay, (const TZ*)beta, ld_beta, cu_q, q_start, state_slot,
-            H, dk, dv, L, chunk, q_scale, vec);
+            H, dk, dv, L, chunk, q_scale, vec, dkz, v_scale);
   return 0;
 }
 
@@ -479,7 +489,7 @@ MS_EXPORT int ms_decay_scan(float* o_out, float* state, const void* q, int ld_q,
                             const void* v, int ld_v, const void* z, int ld_z, const float* z_bias, const float* decay_coef,
                             float z_sign, int z_is_decay, const void* beta, int ld_beta, const int* cu_q, const int* q_start,
                             const int* state_slot, int num_rows, int H, int dk, int dv, float q_scale, int delta, int in_dtype,
-                            int z_dtype, cudaStream_t stream) {
+                            int z_dtype, int decay_per_head, const float* v_scale, cudaStream_t stream) {
   if (num_rows == 0) return 0;
   MS_CHECK_ARG(H > 0 && dk > 0 && dv > 0 && dk <= 32 * SCAN_MAX_KPT, "decay_scan: key size %d is outside 1..%d", dk, 32 * SCAN_MAX_KPT);
   MS_CHECK_ARG(qk_group > 0 && H % qk_group == 0, "decay_scan: %d heads are not a multiple of the group of %d", H, qk_group);
@@ -487,7 +497,7 @@ MS_EXPORT int ms_decay_scan(float* o_out, float* state, const void* q, int ld_q,
   MS_CHECK_ARG(!z_is_decay || z_dtype == MS_F32, "decay_scan: decays worked out beforehand are float32");
 #define MS_SCAN(TIN, TZZ, D)                                                                                                  \
   return launch_scan<TIN, TZZ, D>(num_rows, H, dk, dv, o_out, state, q, ld_q, k, ld_k, qk_group, v, ld_v, z, ld_z, z_bias, decay_coef, z_sign, z_is_decay, \
-                                  beta, ld_beta, cu_q, q_start, state_slot, num_rows, H, dk, dv, q_scale, stream)
+                                  beta, ld_beta, cu_q, q_start, state_slot, num_rows, H, dk, dv, q_scale, decay_per_head ? 1 : dk, v_scale, stream)
   if (in_dtype == MS_F32 && z_dtype == MS_F32) {
     if (delta) MS_SCAN(float, float, true);
     MS_SCAN(float, float, false);
@@ -533,9 +543,11 @@ MS_EXPORT int ms_segment_setup(int* seg_cu, int* seg_zero, int* seg_slot, const 
 // (ms_decay_from_logits), c [T, H * dk] and before [rows * P, H, dv, dk] scratch, ends [rows * P, H, dv, dk] the scan's end states.
 MS_EXPORT int ms_segment_finish(float* o, float* state, const float* ends, float* before, float* c, const float* decay, int ld_decay,
                                 const void* q, int ld_q, int qk_group, const int* seg_cu, const int* q_start, const int* state_slot,
-                                int num_rows, int num_tokens, int P, int H, int dk, int dv, float q_scale, int in_dtype, cudaStream_t stream) {
+                                int num_rows, int num_tokens, int P, int H, int dk, int dv, float q_scale, int in_dtype,
+                                int decay_per_head, cudaStream_t stream) {
   if (num_rows == 0) return 0;
-  const int segments = num_rows * P, width = H * dk;
+  const int dkz = decay_per_head ? 1 : dk;
+  const int segments = num_rows * P, width = H * dkz;
   {
     const long long items = (long long)segments * width;
     MS_LAUNCH(segment_cumprod_kernel, (unsigned)((items + 127) / 128), 128, 0, stream, c, decay, ld_decay, seg_cu, segments, width);
@@ -543,7 +555,7 @@ MS_EXPORT int ms_segment_finish(float* o, float* state, const float* ends, float
   {
     const long long items = (long long)num_rows * H * dv * dk;
     MS_LAUNCH(segment_combine_kernel, (unsigned)((items + 255) / 256), 256, 0, stream, state, ends, before, c, seg_cu, q_start,
-              state_slot, num_rows, P, H, dk, dv);
+              state_slot, num_rows, P, H, dk, dv, dkz);
   }
   int cols = dv;
   while (cols > 1 && ((size_t)cols * (dk + 1) + (size_t)FIX_RUN * dk) * sizeof(float) > 40 * 1024) cols = (cols + 1) / 2;
@@ -554,17 +566,17 @@ MS_EXPORT int ms_segment_finish(float* o, float* state, const float* ends, float
   const dim3 grid(segments, H, (longest + FIX_RUN - 1) / FIX_RUN);
   if (in_dtype == MS_F32)
     MS_LAUNCH(segment_fixup_kernel<float>, grid, FIX_THREADS, smem, stream, o, (const float*)q, ld_q, qk_group, c, before, seg_cu, q_start,
-              P, H, dk, dv, cols, q_scale);
+              P, H, dk, dv, cols, q_scale, dkz);
   else
     MS_LAUNCH(segment_fixup_kernel<__nv_bfloat16>, grid, FIX_THREADS, smem, stream, o, (const __nv_bfloat16*)q, ld_q, qk_group, c, before,
-              seg_cu, q_start, P, H, dk, dv, cols, q_scale);
+              seg_cu, q_start, P, H, dk, dv, cols, q_scale, dkz);
   return 0;
 }
 
 MS_EXPORT int ms_conv_silu_unit(float* out, const void* proj, int ld, const void* conv_state, const float* w,
                                 const int* row_of_token, const int* cu_q, const int* q_start, const int* state_slot,
                                 int num_tokens, int C, int taps, int unit_heads, int dk, int other_heads, int dv, float unit_eps,
-                                int dtype, cudaStream_t stream) {
+                                int dtype, const float* bias, cudaStream_t stream) {
   if (num_tokens == 0) return 0;
   MS_CHECK_ARG(taps >= 1 && C == unit_heads * dk + other_heads * dv, "conv_silu_unit: %d channels are not %d x %d + %d x %d", C,
                unit_heads, dk, other_heads, dv);
@@ -573,11 +585,11 @@ MS_EXPORT int ms_conv_silu_unit(float* out, const void* proj, int ld, const void
   const unsigned blocks = (unsigned)((items + warps - 1) / warps);
   if (dtype == MS_F32)
     MS_LAUNCH(conv_silu_unit_kernel<float>, blocks, warps * 32, 0, stream, out, (const float*)proj, ld, (const float*)conv_state, w,
-              row_of_token, cu_q, q_start, state_slot, num_tokens, C, taps, unit_heads, dk, other_heads, dv, unit_eps);
+              row_of_token, cu_q, q_start, state_slot, num_tokens, C, taps, unit_heads, dk, other_heads, dv, unit_eps, bias);
   else
     MS_LAUNCH(conv_silu_unit_kernel<__nv_bfloat16>, blocks, warps * 32, 0, stream, out, (const __nv_bfloat16*)proj, ld,
               (const __nv_bfloat16*)conv_state, w, row_of_token, cu_q, q_start, state_slot, num_tokens, C, taps, unit_heads, dk,
-              other_heads, dv, unit_eps);
+              other_heads, dv, unit_eps, bias);
   return 0;
 }
 
@@ -608,5 +620,87 @@ MS_EXPORT int ms_head_norm_gate(void* out, int ld_out, const float* o, const flo
   else
     MS_LAUNCH(head_norm_gate_kernel<__nv_bfloat16>, blocks, warps * 32, 0, stream, (__nv_bfloat16*)out, ld_out, o, w,
               (const __nv_bfloat16*)gate, ld_gate, num_tokens, H, dv, eps, scale, gate_kind);
+  return 0;
+}
+
+// ---------------------------------------------------------------- a state-space layer with one decay per head
+// The selective state-space recurrence in its dual form is the decay rule above with one decay for all key channels of a
+// head: S_t = a_t S_(t-1) + (dt_t B_t) x_t^T, y_t = S_t^T C_t + D_h x_t, with dt_t = softplus(raw_t + bias_h) and
+// a_t = exp(-exp(A_h) dt_t). B plays the keys' part, C the queries', x the values' (times dt_t per token and head).
+namespace ms {
+
+// out[0, t, h] = dt = softplus(raw[t, h] + bias[h]); out[1, t, h] = exp(-coef[h] * dt), float32, coef = exp(A_h):
+// two planes of [T, H], each the shape the scan takes (a factor on the values, a decay per head).
+template <typename T>
+__global__ void ssm_step_decay_kernel(float* __restrict__ out, const T* __restrict__ raw, int ld, const float* __restrict__ bias,
+                                      const float* __restrict__ coef, long long items, int H) {
+  pdl_prologue();
+  const long long idx = (long long)blockIdx.x * blockDim.x + threadIdx.x;
+  if (idx >= items) return;
+  const long long t = idx / H;
+  const int h = (int)(idx - t * H);
+  const float dt = softplusf(Elem<T>::load(raw + t * ld + h) + bias[h]);
+  out[idx] = dt;
+  out[items + idx] = expf(-coef[h] * dt);
+}
+
+// y[c] = (o[t, c] + skip[c / dv] * x[t, c]) * silu(gate[t, c]); out[t, c] = y[c] / sqrt(mean over c's part of y^2 + eps) * w[c],
+// the `width` channels of a token cut into `parts` equal parts, each normed by its own root mean square. One CTA per
+// (token, part); float32 arithmetic; sums in a fixed order.
+constexpr int GGN_THREADS = 128;
+template <typename T>
+__global__ void __launch_bounds__(GGN_THREADS)
+gated_group_norm_kernel(T* __restrict__ out, int ld_out, const float* __restrict__ o, const float* __restrict__ x, int ld_x,
+                        const float* __restrict__ skip, const T* __restrict__ gate, int ld_gate, const float* __restrict__ w,
+                        int width, int parts, int dv, float eps) {
+  __shared__ float scratch[32];
+  pdl_prologue();
+  const int t = blockIdx.x / parts, part = blockIdx.x - t * parts;
+  const int size = width / parts, base = part * size;
+  float ss = 0.f;
+  for (int c = threadIdx.x; c < size; c += GGN_THREADS) {
+    const int ch = base + c;
+    const float g = Elem<T>::load(gate + (size_t)t * ld_gate + ch);
+    float y = o[(size_t)t * width + ch];
+    if (skip) y = fmaf(skip[ch / dv], x[(size_t)t * ld_x + ch], y);
+    y *= g / (1.0f + expf(-g));
+    ss += y * y;
+  }
+  ss = block_sum(ss, scratch);
+  const float inv = 1.0f / sqrtf(ss / (float)size + eps);
+  for (int c = threadIdx.x; c < size; c += GGN_THREADS) {
+    const int ch = base + c;
+    const float g = Elem<T>::load(gate + (size_t)t * ld_gate + ch);
+    float y = o[(size_t)t * width + ch];
+    if (skip) y = fmaf(skip[ch / dv], x[(size_t)t * ld_x + ch], y);
+    y *= g / (1.0f + expf(-g));
+    Elem<T>::store(out + (size_t)t * ld_out + ch, (y * inv) * w[ch]);
+  }
+}
+
+}  // namespace ms
+
+MS_EXPORT int ms_ssm_step_decay(float* out, const void* raw, int ld, const float* bias, const float* coef, int num_tokens, int H,
+                                int dtype, cudaStream_t stream) {
+  if (num_tokens == 0) return 0;
+  const long long items = (long long)num_tokens * H;
+  const unsigned blocks = (unsigned)((items + 255) / 256);
+  if (dtype == MS_F32) MS_LAUNCH(ssm_step_decay_kernel<float>, blocks, 256, 0, stream, out, (const float*)raw, ld, bias, coef, items, H);
+  else MS_LAUNCH(ssm_step_decay_kernel<__nv_bfloat16>, blocks, 256, 0, stream, out, (const __nv_bfloat16*)raw, ld, bias, coef, items, H);
+  return 0;
+}
+
+MS_EXPORT int ms_gated_group_norm(void* out, int ld_out, const float* o, const float* x, int ld_x, const float* skip, const void* gate,
+                                  int ld_gate, const float* w, int num_tokens, int width, int parts, int dv, float eps, int dtype,
+                                  cudaStream_t stream) {
+  if (num_tokens == 0) return 0;
+  MS_CHECK_ARG(parts >= 1 && width % parts == 0 && dv >= 1, "gated_group_norm: %d channels in %d parts", width, parts);
+  const unsigned blocks = (unsigned)num_tokens * (unsigned)parts;
+  if (dtype == MS_F32)
+    MS_LAUNCH(gated_group_norm_kernel<float>, blocks, GGN_THREADS, 0, stream, (float*)out, ld_out, o, x, ld_x, skip, (const float*)gate,
+              ld_gate, w, width, parts, dv, eps);
+  else
+    MS_LAUNCH(gated_group_norm_kernel<__nv_bfloat16>, blocks, GGN_THREADS, 0, stream, (__nv_bfloat16*)out, ld_out, o, x, ld_x, skip,
+              (const __nv_bfloat16*)gate, ld_gate, w, width, parts, dv, eps);
   return 0;
 }

@@ -12,10 +12,11 @@ from dataclasses import dataclass
 
 import torch
 
-from . import blas, native
-from .mixers import (add_dyt, add_rmsnorm_scaled, add_row_vector, axpby, channel_gate, conv_silu_unit,  # noqa: F401
-                     conv_state_update, decay_scan, gate_relu_squared, gelu_tanh, head_gate, head_norm_gate, latent_prepare, qkv_prepare,
-                     relu_squared, rope_table_scaled, scale_, stream_concat)
+from . import blas, experts, native
+from .mixers import (act_mul, add_dyt, add_rmsnorm_scaled, add_row_vector, axpby, channel_gate, conv_silu_unit,  # noqa: F401
+                     conv_state_update, decay_scan, gate_relu_squared, gated_group_norm, gelu_tanh, head_gate, head_norm_gate,
+                     latent_prepare, latent_rope_prepare, qkv_prepare, relu_squared, rope_table_scaled, row_rmsnorm, scale_,
+                     ssm_step_decay, stream_concat)
 from .native import NativeError, OutOfBlocks
 
 __all__ = [

@@ -6,6 +6,7 @@ Each *module* is one shared library made from a few source files under ``csrc/``
 - ``kernels``: the CUDA kernels every model needs, for sm_100a;
 - ``mixers``: pointwise kernels of parts that only some models have, compiled when one of them is first used;
 - ``recurrence``: the linear-attention recurrences and what surrounds them, compiled when a model has such a layer;
+- ``experts``: the kernels of a routed feed-forward, compiled when a model has one;
 - further modules are compiled only when a model needs them (for instance the bfloat16
   attention kernels for one head size), so a first call compiles what that model uses.
 
@@ -65,6 +66,7 @@ PREBUILT_HEAD_DIMS = (16, 32, 48, 64, 80, 128, 256)
 # the linear-attention recurrences): compiled when a model first needs one of them
 MIXERS = Module("mixers", ("mixer_pointwise.cu", "block_ops.cu"))
 RECURRENCE = Module("recurrence", ("recurrence.cu",))
+EXPERTS = Module("experts", ("routed_experts.cu",))  # a routed feed-forward: router, plan, the experts' products, the weighted sum
 GEMM_TC = Module("gemm_tc", ("gemm_tc.cu",))
 ATTN_TC = Module("attn_tc", ("attention_tc.cu",))
 
@@ -73,7 +75,7 @@ def all_modules() -> list[Module]:
     """Every module of the package (what ``__graft_entry__.build`` compiles)."""
     from .attention_bf16 import module_for
 
-    return [HOST, KERNELS, MIXERS, RECURRENCE, GEMM_TC, ATTN_TC] + [module_for(d) for d in PREBUILT_HEAD_DIMS]
+    return [HOST, KERNELS, MIXERS, RECURRENCE, EXPERTS, GEMM_TC, ATTN_TC] + [module_for(d) for d in PREBUILT_HEAD_DIMS]
 
 
 def log(msg: str) -> None:

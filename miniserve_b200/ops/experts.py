@@ -1,0 +1,81 @@
+"""Python faces of the kernels in ``csrc/routed_experts.cu``: a router's choice, the plan that sorts a step's
+(token, choice) pairs by expert, the experts' products over the sorted rows, and the weighted sum."""
+
+from __future__ import annotations
+
+import torch
+
+from . import native
+from .mixers import _dt, _f32, _ptr, _rows, _stream
+
+ACTIVATIONS = {"silu": 0, "gelu_tanh": 1}
+
+
+def expert_route(idx, wgt, x, router, correction, top: int, group_count: int, group_keep: int, weight_scale: float,
+                 renormalize: bool, stream=None) -> None:
+    """idx [T, top] int32 and wgt [T, top] float32: each token's chosen router outputs and their weights.
+    Logits ``x router^T`` in float32 (``router`` [R, K] float32), scores their softmax, choice scores the scores plus
+    ``correction`` [R] (float32, or None); the R outputs form ``group_count`` equal groups of neighbours of which the
+    ``group_keep`` with the largest choice score in them can be chosen from; weights are the chosen scores (without
+    the correction) times ``weight_scale``, divided by their sum if ``renormalize``. Ties go to the lower index."""
+    t, k = x.shape
+    r = router.shape[0]
+    _f32(router, correction, wgt)
+    assert router.shape == (r, k) and idx.shape == (t, top) and wgt.shape == (t, top) and idx.dtype == torch.int32
+    assert idx.is_contiguous() and (correction is None or correction.numel() == r)
+    native.experts_check(native.experts().ms_expert_route(
+        _ptr(idx), _ptr(wgt), _ptr(x), _rows(x), _ptr(router), _ptr(correction), t, k, r, top, group_count, group_keep,
+        float(weight_scale), int(renormalize), _dt(x.dtype), _stream(stream)))
+
+
+def expert_max_tiles(slots: int, experts: int) -> int:
+    """The most tiles of sorted rows a step of ``slots`` (token, choice) pairs over ``experts`` experts can have."""
+    return int(native.experts().ms_expert_max_tiles(slots, experts))
+
+
+def expert_plan(pos, perm, offsets, tiles, meta, idx, experts: int, stream=None) -> None:
+    """Sorts the slots of ``idx`` [T, top] by expert, on the device: ``pos`` [T * top] the sorted row of a slot (-1: the
+    slot's choice is not one of the ``experts`` experts with tensors), ``perm`` [T * top] the slot of a sorted row,
+    ``offsets`` [experts + 1], ``tiles`` [max_tiles, 2] = (expert, first row), ``meta`` [2] = (tiles, sorted rows)."""
+    slots = idx.numel()
+    for a in (pos, perm, offsets, tiles, meta, idx):
+        assert a.dtype == torch.int32 and a.is_contiguous() and a.is_cuda
+    assert pos.numel() == slots and perm.numel() == slots and offsets.numel() == experts + 1 and meta.numel() >= 2
+    assert tiles.numel() >= 2 * expert_max_tiles(slots, experts)
+    native.experts_check(native.experts().ms_expert_plan(_ptr(pos), _ptr(perm), _ptr(offsets), _ptr(tiles), _ptr(meta), _ptr(idx),
+                                                         slots, experts, _stream(stream)))
+
+
+def expert_gate_up(out, x, w_gate_up, perm, top: int, tiles, meta, offsets, activation: str, stream=None) -> None:
+    """out [T * top, I] (the run's dtype), row r = act(W_gate[e] h) * (W_up[e] h) with h = x[perm[r] // top] and e the
+    expert whose sorted rows hold r; ``w_gate_up`` [E, 2 I, K]: an expert's gate rows, then its up rows."""
+    slots, inter = out.shape
+    e, two_i, k = w_gate_up.shape
+    assert two_i == 2 * inter and x.shape[1] == k and out.is_contiguous() and w_gate_up.is_contiguous()
+    assert out.dtype == x.dtype == w_gate_up.dtype
+    native.experts_check(native.experts().ms_expert_gemm(
+        _ptr(out), _ptr(x), _rows(x), _ptr(perm), top, _ptr(w_gate_up), _ptr(tiles), _ptr(meta), _ptr(offsets),
+        expert_max_tiles(slots, e), inter, k, 1, ACTIVATIONS[activation], _dt(x.dtype), _stream(stream)))
+
+
+def expert_down(out, act, w_down, tiles, meta, offsets, stream=None) -> None:
+    """out [T * top, H] float32, row r = W_down[e] act[r] over the sorted rows; ``w_down`` [E, H, I]."""
+    slots, hidden = out.shape
+    e, h, inter = w_down.shape
+    _f32(out)
+    assert h == hidden and act.shape == (slots, inter) and act.is_contiguous() and w_down.is_contiguous() and act.dtype == w_down.dtype
+    native.experts_check(native.experts().ms_expert_gemm(
+        _ptr(out), _ptr(act), inter, None, 1, _ptr(w_down), _ptr(tiles), _ptr(meta), _ptr(offsets),
+        expert_max_tiles(slots, e), hidden, inter, 0, 0, _dt(act.dtype), _stream(stream)))
+
+
+def expert_combine(out, y, x, idx, wgt, pos, experts: int, stream=None) -> None:
+    """out[t] = sum over the token's choices, in their order, of wgt * (y[pos] for an expert with tensors, x[t] for a
+    router output from ``experts`` on: an identity expert); float32 sum, one rounding."""
+    t, hidden = out.shape
+    top = idx.shape[1]
+    _f32(y, wgt)
+    assert out.is_contiguous() and x.shape == (t, hidden) and x.dtype == out.dtype and y.shape[1] == hidden
+    native.experts_check(native.experts().ms_expert_combine(
+        _ptr(out), _ptr(y), _ptr(x), _rows(x), _ptr(idx), _ptr(wgt), _ptr(pos), t, hidden, top, experts, _dt(out.dtype),
+        _stream(stream)))

@@ -104,21 +104,26 @@ def qkv_prepare(q_out, k_pool, v_pool, q, k, v, q_norm_w, k_norm_w, cos_sin, rot
 
 
 def decay_scan(o_out, state, q, k, v, z, z_bias, decay_coef, z_sign: float, beta, ctx, heads: int, dk: int, dv: int,
-               q_scale: float, delta: bool) -> None:
+               q_scale: float, delta: bool, head_decay: bool = False, v_scale=None) -> None:
     """The token-by-token recurrence of every row of the step (``csrc/recurrence.cu``), from each
     request's slot of ``state`` [slots, heads, dv, dk] float32 (zero where a row starts at position 0)
     and back into it; o_out [T, heads, dv] float32. q, k [T, groups*dk], v [T, heads*dv], z [T, heads*dk]
-    and beta [T, heads] are 2-d views; z_bias [heads*dk], decay_coef [heads] float32."""
+    and beta [T, heads] are 2-d views; z_bias [heads*dk], decay_coef [heads] float32.
+    ``head_decay``: z [T, heads] float32 holds the decays themselves, one for all key channels of a head and token
+    (z_bias, decay_coef and z_sign are not used). ``v_scale`` [T, heads] float32: v counts times it, per token and head."""
     t = o_out.shape[0]
-    _f32(o_out, state, z_bias, decay_coef)
+    _f32(o_out, state, z_bias, decay_coef, v_scale)
     assert o_out.shape == (t, heads, dv) and state.shape[1:] == (heads, dv, dk)
     groups = q.shape[1] // dk
-    assert q.shape == (t, groups * dk) and k.shape == q.shape and v.shape == (t, heads * dv) and z.shape == (t, heads * dk)
+    assert q.shape == (t, groups * dk) and k.shape == q.shape and v.shape == (t, heads * dv)
+    assert z.shape == (t, heads if head_decay else heads * dk) and (not head_decay or (z.dtype == torch.float32 and not delta))
     assert q.dtype == k.dtype == v.dtype and (beta is None or beta.dtype == z.dtype)
+    assert v_scale is None or v_scale.shape == (t, heads)
     if not delta and not ctx.decode_only and t >= SEGMENT_MIN_TOKENS and SEGMENTS > 1:
-        return _decay_scan_segmented(o_out, state, q, k, v, z, z_bias, decay_coef, z_sign, ctx, heads, dk, dv, q_scale)
-    ready = 0
-    if not ctx.decode_only:
+        return _decay_scan_segmented(o_out, state, q, k, v, z, z_bias, decay_coef, z_sign, ctx, heads, dk, dv, q_scale, head_decay,
+                                     v_scale)
+    ready = int(head_decay)
+    if not ctx.decode_only and not head_decay:
         # a prompt portion: exponentials and logarithms for all tokens at once, not inside the serial walk
         # (a decode step, one token a row, works them out while it stages the token)
         width = heads * dk + (heads if beta is not None else 0)
@@ -131,21 +136,24 @@ def decay_scan(o_out, state, q, k, v, z, z_bias, decay_coef, z_sign: float, beta
         _ptr(o_out), _ptr(state), _ptr(q), _rows(q), _ptr(k), _rows(k), heads // groups, _ptr(v), _rows(v), _ptr(z), _rows(z),
         _ptr(z_bias), _ptr(decay_coef), float(z_sign), ready, _ptr(beta), 0 if beta is None else _rows(beta), _ptr(ctx.cu_q),
         _ptr(ctx.q_start), _ptr(ctx.state_slot), ctx.num_rows, heads, dk, dv, float(q_scale), int(delta), _dt(q.dtype),
-        _dt(z.dtype), ctx.stream))
+        _dt(z.dtype), int(head_decay), _ptr(v_scale), ctx.stream))
 
 
-def conv_silu_unit(out, x, conv_state, weight, ctx, unit_heads: int, dk: int, other_heads: int, dv: int, unit_eps: float) -> None:
+def conv_silu_unit(out, x, conv_state, weight, ctx, unit_heads: int, dk: int, other_heads: int, dv: int, unit_eps: float,
+                   bias=None) -> None:
     """out [T, C] float32 = SiLU(causal convolution over time of the C channels ``x`` [T, C], a view),
     the first ``unit_heads`` heads of dk channels then divided by sqrt(sum of squares + unit_eps).
-    ``weight`` [C, taps] float32; ``conv_state`` [slots, taps - 1, C] holds each request's last inputs."""
+    ``weight`` [C, taps] float32 (``bias`` [C] float32 is added if given); ``conv_state`` [slots, taps - 1, C] holds each
+    request's last inputs."""
     t, c = out.shape
     taps = weight.shape[1]
-    _f32(out, weight)
+    _f32(out, weight, bias)
+    assert bias is None or bias.numel() == c
     assert x.shape == (t, c) and weight.shape[0] == c and conv_state.dtype == x.dtype and conv_state.is_contiguous()
     assert conv_state.shape[1:] == (max(taps - 1, 0), c)
     native.recurrence_check(native.recurrence().ms_conv_silu_unit(
         _ptr(out), _ptr(x), _rows(x), _ptr(conv_state), _ptr(weight), _ptr(ctx.row_of_token), _ptr(ctx.cu_q), _ptr(ctx.q_start),
-        _ptr(ctx.state_slot), t, c, taps, unit_heads, dk, other_heads, dv, float(unit_eps), _dt(x.dtype), ctx.stream))
+        _ptr(ctx.state_slot), t, c, taps, unit_heads, dk, other_heads, dv, float(unit_eps), _dt(x.dtype), _ptr(bias), ctx.stream))
 
 
 def conv_state_update(conv_state, x, ctx, taps: int) -> None:
@@ -164,7 +172,8 @@ SEGMENTS = 8
 SEGMENT_MIN_TOKENS = 512
 
 
-def _decay_scan_segmented(o_out, state, q, k, v, z, z_bias, decay_coef, z_sign, ctx, heads, dk, dv, q_scale) -> None:
+def _decay_scan_segmented(o_out, state, q, k, v, z, z_bias, decay_coef, z_sign, ctx, heads, dk, dv, q_scale, head_decay=False,
+                          v_scale=None) -> None:
     from types import SimpleNamespace
 
     t, dev, p, rows = o_out.shape[0], o_out.device, SEGMENTS, ctx.num_rows
@@ -178,22 +187,50 @@ def _decay_scan_segmented(o_out, state, q, k, v, z, z_bias, decay_coef, z_sign, 
         if hasattr(ctx, "step_cache"):
             ctx.step_cache[key] = seg
     seg_cu, seg_zero, seg_slot = seg
-    decay = ctx.buffer("scan.decay", (t, heads * dk), torch.float32, dev)
-    native.recurrence_check(lib.ms_decay_from_logits(_ptr(decay), _ptr(z), _rows(z), _ptr(z_bias), _ptr(decay_coef), float(z_sign), None, 0,
-                                                 t, heads, dk, _dt(z.dtype), ctx.stream))
+    dkz = 1 if head_decay else dk
+    if head_decay:
+        decay = z
+    else:
+        decay = ctx.buffer("scan.decay", (t, heads * dk), torch.float32, dev)
+        native.recurrence_check(lib.ms_decay_from_logits(_ptr(decay), _ptr(z), _rows(z), _ptr(z_bias), _ptr(decay_coef), float(z_sign),
+                                                         None, 0, t, heads, dk, _dt(z.dtype), ctx.stream))
     ends = ctx.buffer("scan.ends", (rows * p, heads, dv, dk), torch.float32, dev)
     before = ctx.buffer("scan.before", (rows * p, heads, dv, dk), torch.float32, dev)
-    cum = ctx.buffer("scan.cum", (t, heads * dk), torch.float32, dev)
+    cum = ctx.buffer("scan.cum", (t, heads * dkz), torch.float32, dev)
     pieces = SimpleNamespace(cu_q=seg_cu, q_start=seg_zero, state_slot=seg_slot, num_rows=rows * p, stream=ctx.stream)
     groups = q.shape[1] // dk
     native.recurrence_check(lib.ms_decay_scan(
         _ptr(o_out), _ptr(ends), _ptr(q), _rows(q), _ptr(k), _rows(k), heads // groups, _ptr(v), _rows(v), _ptr(decay), _rows(decay),
         _ptr(z_bias), _ptr(decay_coef), float(z_sign), 1, None, 0, _ptr(pieces.cu_q), _ptr(pieces.q_start), _ptr(pieces.state_slot),
-        pieces.num_rows, heads, dk, dv, float(q_scale), 0, _dt(q.dtype), 0, ctx.stream))
+        pieces.num_rows, heads, dk, dv, float(q_scale), 0, _dt(q.dtype), 0, int(head_decay), _ptr(v_scale), ctx.stream))
     native.recurrence_check(lib.ms_segment_finish(
         _ptr(o_out), _ptr(state), _ptr(ends), _ptr(before), _ptr(cum), _ptr(decay), _rows(decay), _ptr(q), _rows(q), heads // groups,
-        _ptr(seg_cu), _ptr(ctx.q_start), _ptr(ctx.state_slot), rows, t, p, heads, dk, dv, float(q_scale), _dt(q.dtype), ctx.stream),
-        launches=3)
+        _ptr(seg_cu), _ptr(ctx.q_start), _ptr(ctx.state_slot), rows, t, p, heads, dk, dv, float(q_scale), _dt(q.dtype), int(head_decay),
+        ctx.stream), launches=3)
+
+
+def ssm_step_decay(out, raw, bias, coef, stream=None) -> None:
+    """out [2, T, H] float32: out[0] the step sizes softplus(raw[t, h] + bias[h]), out[1] the decays
+    exp(-coef[h] * step size); ``raw`` [T, H] a view, bias and coef float32 [H]."""
+    t, h = raw.shape
+    _f32(out, bias, coef)
+    assert out.shape == (2, t, h) and bias.numel() == h and coef.numel() == h
+    native.recurrence_check(native.recurrence().ms_ssm_step_decay(_ptr(out), _ptr(raw), _rows(raw), _ptr(bias), _ptr(coef), t, h,
+                                                                  _dt(raw.dtype), _stream(stream)))
+
+
+def gated_group_norm(out, o, x, skip, gate, weight, parts: int, dv: int, eps: float, stream=None) -> None:
+    """y = (o + skip[head] * x) * silu(gate) over the ``width`` channels of a token (head = channel // dv), then each of
+    ``parts`` equal parts of y divided by its own root mean square, times ``weight`` [width]. ``o`` [T, width] float32;
+    ``x`` [T, width] float32 (a view) and ``skip`` [heads] float32, or both None; ``out`` and ``gate`` 2-d views in the
+    run's dtype. The gate comes before the norm."""
+    t, width = o.shape
+    _f32(o, weight, skip)
+    assert out.shape == (t, width) and gate.shape == (t, width) and gate.dtype == out.dtype and weight.numel() == width
+    assert (x is None) == (skip is None) and (x is None or (x.shape == (t, width) and x.dtype == torch.float32))
+    native.recurrence_check(native.recurrence().ms_gated_group_norm(
+        _ptr(out), _rows(out), _ptr(o), _ptr(x), 0 if x is None else _rows(x), _ptr(skip), _ptr(gate), _rows(gate), _ptr(weight), t,
+        width, parts, dv, float(eps), _dt(out.dtype), _stream(stream)))
 
 
 GATE_KINDS = {"silu": 0, "sigmoid": 1}
@@ -296,3 +333,47 @@ def latent_prepare(pool, latent, weight, eps: float, positions, row_of_token, pa
     native.mixers_check(native.mixers().ms_latent_prepare(
         _ptr(pool), _ptr(latent), _rows(latent), 0, _ptr(weight), float(eps), _ptr(positions), _ptr(row_of_token), _ptr(page_indptr),
         _ptr(page_indices), t, rank, pool.shape[3], page_size, pool.shape[0], _ptr(status), _dt(latent.dtype), _stream(stream)))
+
+
+def row_rmsnorm(out, x, weight, eps: float, stream=None) -> None:
+    """out[t] = x[t] / sqrt(mean x[t]^2 + eps) * weight over the columns of 2-d views ``x`` and ``out`` (rows may be part
+    of wider ones); float32 statistics, ``weight`` float32."""
+    _f32(weight)
+    t, n = x.shape
+    assert out.shape == (t, n) and out.dtype == x.dtype and weight.numel() == n
+    native.mixers_check(native.mixers().ms_row_rmsnorm(_ptr(out), _rows(out), _ptr(x), _rows(x), _ptr(weight), t, n, float(eps),
+                                                       _dt(x.dtype), _stream(stream)))
+
+
+def latent_rope_prepare(pool, kv, weight, eps: float, q, q_dim: int, q_out, cos_sin, positions, row_of_token, page_indptr, page_indices,
+                        page_size: int, status, stream=None) -> None:
+    """What latent attention with a rotated part caches and asks with. ``kv`` [T, R + rot] (a view into a projection's
+    rows): its first R columns over their root mean square, times the float32 ``weight`` [R], and its last rot columns
+    turned by the token's position (``cos_sin`` float32 [T, rot]: cosines of the pairs (i, i + rot / 2), then sines), go
+    into the token's slot of ``pool`` [pages, 1, page_size, D] side by side, zeros behind. ``q`` [T, H, q_dim + rot]
+    contiguous: every head's last rot channels, turned likewise, go to ``q_out`` [T, H, D] at columns R .. R + rot
+    (zeros behind); the first R columns of ``q_out`` are the caller's."""
+    _f32(weight, cos_sin)
+    t, width = kv.shape
+    rot = cos_sin.shape[1]
+    rank = width - rot
+    heads = q.shape[1]
+    d = pool.shape[3]
+    assert pool.dim() == 4 and pool.shape[1] == 1 and pool.shape[2] == page_size and d >= width and pool.dtype == kv.dtype
+    assert weight.numel() == rank and cos_sin.shape == (t, rot) and q.is_contiguous() and q.shape == (t, heads, q_dim + rot)
+    assert q_out.is_contiguous() and q_out.shape == (t, heads, d) and q.dtype == kv.dtype == q_out.dtype
+    native.mixers_check(native.mixers().ms_latent_rope_prepare(
+        _ptr(pool), _ptr(kv), _rows(kv), _ptr(weight), float(eps), _ptr(q), heads * (q_dim + rot), heads, q_dim, _ptr(q_out),
+        _ptr(cos_sin), _ptr(positions), _ptr(row_of_token), _ptr(page_indptr), _ptr(page_indices), t, rank, rot, d, page_size,
+        pool.shape[0], _ptr(status), _dt(kv.dtype), _stream(stream)))
+
+
+ACTIVATIONS = {"silu": 0, "gelu_tanh": 1}
+
+
+def act_mul(out, gate_up, activation: str, stream=None) -> None:
+    """out[t, c] = act(gate_up[t, c]) * gate_up[t, I + c], act SiLU or the tanh form of GELU, computed in float32."""
+    t, inter = out.shape
+    assert out.is_contiguous() and gate_up.is_contiguous() and gate_up.shape == (t, 2 * inter) and gate_up.dtype == out.dtype
+    native.mixers_check(native.mixers().ms_act_mul(_ptr(out), _ptr(gate_up), t, inter, ACTIVATIONS[activation], _dt(out.dtype),
+                                                   _stream(stream)))

@@ -137,6 +137,9 @@ def mixers():
     _declare(lib, "ms_gate_relu_squared", [_p, _i, _p, _p, _i, _p, _i, _i, _i, _i, _i, _i, _i, _p])
     _declare(lib, "ms_rope_table_scaled", [_p, _p, _p, _f, _i, _i, _p])
     _declare(lib, "ms_latent_prepare", [_p, _p, _i, _i, _p, _f, _p, _p, _p, _p, _i, _i, _i, _i, _i, _p, _i, _p])
+    _declare(lib, "ms_row_rmsnorm", [_p, _i, _p, _i, _p, _i, _i, _f, _i, _p])
+    _declare(lib, "ms_latent_rope_prepare", [_p, _p, _i, _p, _f, _p, _i, _i, _i, _p, _p, _p, _p, _p, _p, _i, _i, _i, _i, _i, _i, _p, _i, _p])
+    _declare(lib, "ms_act_mul", [_p, _p, _i, _i, _i, _i, _p])
     return lib
 
 
@@ -147,14 +150,34 @@ def recurrence():
     _declare(lib, "ms_recurrence_set_pdl", [_i], None)
     lib.ms_recurrence_set_pdl(int(pdl_enabled()))
     _declare(lib, "ms_decay_scan", [_p, _p, _p, _i, _p, _i, _i, _p, _i, _p, _i, _p, _p, _f, _i, _p, _i, _p, _p, _p,
-                                    _i, _i, _i, _i, _f, _i, _i, _i, _p])
+                                    _i, _i, _i, _i, _f, _i, _i, _i, _i, _p, _p])
     _declare(lib, "ms_segment_setup", [_p, _p, _p, _p, _i, _i, _p])
-    _declare(lib, "ms_segment_finish", [_p, _p, _p, _p, _p, _p, _i, _p, _i, _i, _p, _p, _p, _i, _i, _i, _i, _i, _i, _f, _i, _p])
+    _declare(lib, "ms_segment_finish", [_p, _p, _p, _p, _p, _p, _i, _p, _i, _i, _p, _p, _p, _i, _i, _i, _i, _i, _i, _f, _i, _i, _p])
     _declare(lib, "ms_decay_from_logits", [_p, _p, _i, _p, _p, _f, _p, _i, _i, _i, _i, _i, _p])
-    _declare(lib, "ms_conv_silu_unit", [_p, _p, _i, _p, _p, _p, _p, _p, _p, _i, _i, _i, _i, _i, _i, _i, _f, _i, _p])
+    _declare(lib, "ms_conv_silu_unit", [_p, _p, _i, _p, _p, _p, _p, _p, _p, _i, _i, _i, _i, _i, _i, _i, _f, _i, _p, _p])
+    _declare(lib, "ms_ssm_step_decay", [_p, _p, _i, _p, _p, _i, _i, _i, _p])
+    _declare(lib, "ms_gated_group_norm", [_p, _i, _p, _p, _i, _p, _p, _i, _p, _i, _i, _i, _i, _f, _i, _p])
     _declare(lib, "ms_conv_state_update", [_p, _p, _i, _p, _p, _p, _i, _i, _i, _i, _p])
     _declare(lib, "ms_head_norm_gate", [_p, _i, _p, _p, _p, _i, _i, _i, _i, _f, _f, _i, _i, _p])
     return lib
+
+
+@lru_cache(maxsize=None)
+def experts():
+    lib = ctypes.CDLL(str(build.ensure_built(build.EXPERTS)))
+    _declare(lib, "ms_experts_last_error", [], c_char_p)
+    _declare(lib, "ms_experts_set_pdl", [_i], None)
+    lib.ms_experts_set_pdl(int(pdl_enabled()))
+    _declare(lib, "ms_expert_route", [_p, _p, _p, _i, _p, _p, _i, _i, _i, _i, _i, _i, _f, _i, _i, _p])
+    _declare(lib, "ms_expert_max_tiles", [_i, _i])
+    _declare(lib, "ms_expert_plan", [_p, _p, _p, _p, _p, _p, _i, _i, _p])
+    _declare(lib, "ms_expert_gemm", [_p, _p, _i, _p, _i, _p, _p, _p, _p, _i, _i, _i, _i, _i, _i, _p])
+    _declare(lib, "ms_expert_combine", [_p, _p, _p, _i, _p, _p, _p, _i, _i, _i, _i, _i, _p])
+    return lib
+
+
+def experts_check(rc: int, launches: int = 1) -> None:
+    kernel_check(rc, lib=experts() if rc else None, errfn="ms_experts_last_error", launches=launches)
 
 
 def recurrence_check(rc: int, launches: int = 1) -> None:

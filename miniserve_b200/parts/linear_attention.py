@@ -210,3 +210,109 @@ class GatedDeltaRule(Part):
         feat = ctx.buffer("delta.feat", (t, self.feature_width), dt, dev)
         self.features(x, ctx, cache, feat)
         return ops.linear(feat, self.w_o, stream=ctx.stream, out=ctx.buffer("delta.proj", (t, self.hidden), dt, dev))
+
+
+def _conv_unit(channels: int) -> int:
+    """How many channels one warp of the convolution kernel takes: the largest divisor of ``channels`` up to 128."""
+    for u in range(min(channels, 128), 0, -1):
+        if channels % u == 0:
+            return u
+    return 1
+
+
+@register_part("mixer", "mamba2")
+class SelectiveStateSpace(Part):
+    """A selective state-space layer in its dual (linear-attention) form: per head a matrix state S [state, head_dim],
+
+        dt_t = softplus(raw_t + dt_bias_h),   a_t = exp(-exp(A_log_h) dt_t)          (float32)
+        S_t = a_t S_(t-1) + dt_t B_t x_t^T,   y_t = S_t^T C_t + D_h x_t
+
+    with one decay for the whole head, B and C shared by the heads of a group (head h reads group
+    h // (heads / groups)). One product makes [z | x | B | C | raw dt]; x, B and C pass a short causal convolution per
+    channel (with a bias) and SiLU; y of all heads times silu(z), then divided by its root mean square in
+    ``norm_groups`` equal parts, times a weight, then the output projection. The recurrence is the decay rule of
+    ``csrc/recurrence.cu`` with B as keys, C as queries and x (times dt per token and head) as values. The state and
+    everything that enters it besides the convolution's output are float32; the convolution's last taps - 1 inputs
+    are state beside S.
+    Parameters: ``hidden``, ``heads``, ``head_dim``, ``state``, ``groups``, ``conv`` (taps), ``norm_groups``, ``eps``,
+    ``names`` (input, conv, conv_bias, dt_bias, a_log, skip, norm, o -> tensor names)."""
+    shape_static = True
+    NAMES = dict(input="in_proj.weight", conv="conv1d.weight", conv_bias="conv1d.bias", dt_bias="dt_bias", a_log="A_log",
+                 skip="D", norm="norm.weight", o="out_proj.weight")
+
+    def __init__(self, spec, env):
+        super().__init__(spec, env)
+        self.hidden = param(spec, "hidden", int)
+        self.heads = param(spec, "heads", int)
+        self.dv = param(spec, "head_dim", int)
+        self.n = param(spec, "state", int)
+        self.groups = param(spec, "groups", int)
+        self.taps = param(spec, "conv", int)
+        self.norm_groups = int(spec.get("norm_groups", 1))
+        self.eps = param(spec, "eps", float)
+        self.names = {**self.NAMES, **dict(spec.get("names") or {})}
+        if self.heads % self.groups:
+            raise ValueError(f"{self.heads} heads are not a multiple of {self.groups} groups")
+        self.inner = self.heads * self.dv
+        if self.inner % self.norm_groups:
+            raise ValueError(f"{self.inner} channels do not split into {self.norm_groups} equal parts")
+        if self.taps < 1:
+            raise ValueError(f"the convolution needs at least one tap, got {self.taps}")
+        self.channels = self.inner + 2 * self.groups * self.n  # what passes the convolution: x | B | C
+        self.proj_rows = 2 * self.inner + 2 * self.groups * self.n + self.heads
+        self.feature_width = self.inner
+
+    def cache_need(self):
+        state = FixedState((self.heads, self.dv, self.n), torch.float32)
+        if self.taps == 1:
+            return state
+        return (state, FixedState((self.taps - 1, self.channels), self.env.dtype))
+
+    def weights(self):
+        n, f32 = self.names, dict(precision="float32")
+        return {n["input"]: WeightDecl((self.proj_rows, self.hidden)),
+                n["conv"]: WeightDecl((self.channels, self.taps), **f32), n["conv_bias"]: WeightDecl((self.channels,), **f32),
+                n["dt_bias"]: WeightDecl((self.heads,), **f32), n["a_log"]: WeightDecl((self.heads,), **f32),
+                n["skip"]: WeightDecl((self.heads,), init="ones_normal", **f32),
+                n["norm"]: WeightDecl((self.inner,), init="ones_normal", **f32),
+                n["o"]: WeightDecl((self.hidden, self.inner))}
+
+    def bind(self, tensors):
+        n = self.names
+        self.w_in = _pad_rows(tensors[n["input"]], _pad8(self.proj_rows))
+        self.w_conv = tensors[n["conv"]].float().contiguous()
+        self.w_conv_bias = tensors[n["conv_bias"]].float().contiguous()
+        self.w_dt_bias = tensors[n["dt_bias"]].float().contiguous()
+        self.decay_coef = torch.exp(tensors[n["a_log"]].float()).contiguous()
+        self.w_skip = tensors[n["skip"]].float().contiguous()
+        self.w_norm = tensors[n["norm"]].float().contiguous()
+        self.w_o = tensors[n["o"]].contiguous()
+
+    def features(self, x: torch.Tensor, ctx, cache, out: torch.Tensor, scale: float = 1.0) -> None:
+        if scale != 1.0:
+            raise NotImplementedError("mamba2 hands its features on unscaled")
+        t, dt, dev = x.shape[0], self.env.dtype, self.w_o.device
+        h, g, n, dv, c, inner = self.heads, self.groups, self.n, self.dv, self.channels, self.inner
+        state, conv = (cache if isinstance(cache, tuple) else (cache, None))
+        proj = ops.linear(x, self.w_in, stream=ctx.stream, out=ctx.buffer("ssm.in", (t, self.w_in.shape[0]), dt, dev))
+        xbc_in = proj[:, inner:inner + c]
+        xbc = ctx.buffer("ssm.xbc", (t, c), torch.float32, dev)
+        conv_state = conv.state if conv is not None else ctx.buffer("ssm.noconv", (1, 0, c), dt, dev)
+        unit = _conv_unit(c)
+        ops.conv_silu_unit(xbc, xbc_in, conv_state, self.w_conv, ctx, 0, 1, c // unit, unit, 0.0, bias=self.w_conv_bias)
+        if conv is not None:
+            ops.conv_state_update(conv_state, xbc_in, ctx, self.taps)
+        steps = ctx.buffer("ssm.dt", (2, t, h), torch.float32, dev)  # step sizes, then decays
+        ops.ssm_step_decay(steps, proj[:, inner + c:inner + c + h], self.w_dt_bias, self.decay_coef, stream=ctx.stream)
+        o = ctx.buffer("ssm.o", (t, h, dv), torch.float32, dev)
+        xs, bs, cs = xbc[:, :inner], xbc[:, inner:inner + g * n], xbc[:, inner + g * n:]
+        ops.decay_scan(o, state.state, cs, bs, xs, steps[1], None, self.decay_coef, 1.0, None, ctx, h, n, dv, 1.0, delta=False,
+                       head_decay=True, v_scale=steps[0])
+        ops.gated_group_norm(out, o.view(t, inner), xs, self.w_skip, proj[:, :inner], self.w_norm, self.norm_groups, dv, self.eps,
+                             stream=ctx.stream)
+
+    def forward(self, x, ctx, cache):
+        t, dt, dev = x.shape[0], self.env.dtype, self.w_o.device
+        feat = ctx.buffer("ssm.feat", (t, self.feature_width), dt, dev)
+        self.features(x, ctx, cache, feat)
+        return ops.linear(feat, self.w_o, stream=ctx.stream, out=ctx.buffer("ssm.proj", (t, self.hidden), dt, dev))
