@@ -23,7 +23,9 @@ Qwen3-1.7B) beside the Qwen3 model of the same width, depth, feed-forward size a
 2,048-token prompt step and decode steps at batch 8 behind 2,048 tokens; ``--kernels`` adds the device
 time per kernel of both steps. ``--config mugipel`` does the same for the Mugipel design (attention layers
 with capped scores, a block mask and learned sinks in turn with latent-attention layers, the last stretch of
-layers run twice).
+layers run twice). ``--config rofozen`` does the same for the Rofozen design (state-space layers with one decay
+per head, every fourth layer latent attention with a rotated key part, a window and learned sinks; routed experts
+in every other layer), beside Qwen3 and beside Fekulix, the framework's other design with recurrent layers.
 """
 
 from __future__ import annotations
@@ -367,6 +369,27 @@ def mugipel_config(width: int, ff: int, runs: int, vocab: int, heads: int, kv_he
             "loop": {"start": stored - 4, "stop": stored, "times": 2}}
 
 
+def rofozen_config(width: int, ff: int, runs: int, vocab: int, heads: int, kv_heads: int) -> dict:
+    """A Rofozen model at a real model's layer sizes: three state-space layers (2 * width inner channels in heads of
+    64, a state of 128 per head, 8 groups, 4 taps) to one latent-attention layer (the Qwen3 model's number of heads; 128
+    query and key channels a head, of which 32 or 64 are rotated; a cache entry of max(128, width / 8) numbers, of
+    which a quarter is the rotated key part; a window of 1,024; learned sinks); the feed-forward is dense in even layers and 14
+    experts of ff / 4 with 2 identity experts, 4 of them per token out of 2 of 4 groups, in odd ones (the products of
+    a token equal the dense layer's)."""
+    entry = max(128, width // 8)
+    rot = entry // 4
+    ssm = {"conv": 4, "groups": 8, "heads": 2 * width // 64, "norm_groups": 8, "state": 128, "vdim": 64}
+    lat = {"dim": 128 - rot, "heads": heads, "kv_rank": entry - rot, "q_rank": width // 2, "rot_dim": rot, "scale": 128 ** -0.5, "vdim": 128,
+           "mask": {"size": 1024},
+           "rot": {"base": 1e6, "dims": rot, "scaling": {"factor": 4.0, "fast": 24.0, "original": 8192, "slow": 2.0}}}
+    dense = {"ff": ff, "kind": "dense"}
+    moe = {"kind": "moe", "expert": {"ff": ff // 4},
+           "router": {"experts": 14, "identity": 2, "scale": 2.0, "top": 4, "groups": {"count": 4, "keep": 2}}}
+    layers = [{"type": "latent_attention" if i % 4 == 3 else "mamba2", "mixer": dict(lat if i % 4 == 3 else ssm),
+               "mlp": dict(moe if i % 2 else dense)} for i in range(runs)]
+    return {"architecture": "Rofozen", "width": width, "vocab": vocab, "norm": {"eps": 1e-6}, "layers": layers}
+
+
 def bytes_per_step_of_weights(model) -> int:
     """Bytes of weights a step reads: every run of a layer reads that layer's tensors (a layer that runs twice
     counts twice), plus the norm before the head, the head and the parts between layers."""
@@ -415,7 +438,7 @@ def kernel_times(run_step, repeats: int = 3) -> dict:
 
 
 def run_fekulix(args, design: str = "fekulix") -> dict:
-    """Prefill and decode of a design (Fekulix, Mugipel) beside Qwen3 at equal width, depth, feed-forward and vocabulary."""
+    """Prefill and decode of a design (Fekulix, Mugipel, Rofozen) beside Qwen3 at equal width, depth, feed-forward and vocabulary."""
     import torch
 
     from miniserve_b200.config import preset
@@ -423,7 +446,7 @@ def run_fekulix(args, design: str = "fekulix") -> dict:
     from miniserve_b200.engine.step import StepRow
 
     peaks = load_peaks()
-    make = {"fekulix": fekulix_config, "mugipel": mugipel_config}[design]
+    make = {"fekulix": fekulix_config, "mugipel": mugipel_config, "rofozen": rofozen_config}[design]
     out = {"impl": "ours", "config": design, "dtype": "bf16", "data": "synthetic (random-init weights, uniform token ids)",
            "batch": args.batch, "context": CONTEXT, "prefill_tokens": PREFILL_TOKENS, "peaks": peaks["source"], "sizes": {}}
     steps = min(args.steps, 64)
@@ -434,7 +457,11 @@ def run_fekulix(args, design: str = "fekulix") -> dict:
         f = make(q["hidden_size"], q["intermediate_size"], q["num_hidden_layers"], q["vocab_size"],
                  q["num_attention_heads"], q["num_key_value_heads"])
         entry = {}
-        for name, raw in ((design, f), ("qwen3", q)):
+        beside = [("qwen3", q)]
+        if design == "rofozen":  # the framework's other design with recurrent layers, at the same sizes
+            beside.append(("fekulix", fekulix_config(q["hidden_size"], q["intermediate_size"], q["num_hidden_layers"], q["vocab_size"],
+                                                     q["num_attention_heads"], q["num_key_value_heads"])))
+        for name, raw in [(design, f)] + beside:
             llm = LLM(random=raw, weights_seed=0, dtype="bfloat16", kv_pool_tokens=10 * (CONTEXT + steps + 64) + 4096, page_size=16,
                       max_running=16, chunked_prefill_size=2048, cuda_graph=not args.no_graph)
             eng = llm.engine
@@ -465,6 +492,9 @@ def run_fekulix(args, design: str = "fekulix") -> dict:
             torch.cuda.empty_cache()
         entry["decode_ratio"] = round(entry[design]["decode_tok_s"] / entry["qwen3"]["decode_tok_s"], 3)
         entry["prefill_ratio"] = round(entry[design]["prefill_tok_s"] / entry["qwen3"]["prefill_tok_s"], 3)
+        for name, _ in beside[1:]:
+            entry[f"decode_ratio_{name}"] = round(entry[design]["decode_tok_s"] / entry[name]["decode_tok_s"], 3)
+            entry[f"prefill_ratio_{name}"] = round(entry[design]["prefill_tok_s"] / entry[name]["prefill_tok_s"], 3)
         out["sizes"][size] = entry
     return out
 
@@ -641,10 +671,10 @@ def main() -> int:
     ap.add_argument("--no-graph", action="store_true", help="run decode steps without CUDA graphs")
     ap.add_argument("--profile-range", action="store_true",
                     help="bracket the timed steps with cudaProfilerStart/Stop (for ncu --profile-from-start off)")
-    ap.add_argument("--config", choices=["0.6b", "8b", "32b", "fekulix", "mugipel"], default="0.6b",
+    ap.add_argument("--config", choices=["0.6b", "8b", "32b", "fekulix", "mugipel", "rofozen"], default="0.6b",
                     help="0.6b: the benchmark line; 8b, 32b: the larger workloads through Engine.generate (a line of their own); "
-                         "fekulix, mugipel: prefill and decode of that design beside Qwen3 at equal sizes (a line of its own)")
-    ap.add_argument("--kernels", action="store_true", help="with --config fekulix or mugipel: also device time per kernel of a prompt step and a decode step")
+                         "fekulix, mugipel, rofozen: prefill and decode of that design beside Qwen3 at equal sizes (a line of its own)")
+    ap.add_argument("--kernels", action="store_true", help="with --config fekulix, mugipel or rofozen: also device time per kernel of a prompt step and a decode step")
     ap.add_argument("--only", choices=["all", "decode", "prefill"], default="all",
                     help="measure only the decode steps or only the prefill (for profiling); the line then lacks the other parts")
     args = ap.parse_args()
@@ -657,7 +687,7 @@ def main() -> int:
         args.warmup = 3
     global PROFILE_RANGE
     PROFILE_RANGE = args.profile_range
-    if args.config in ("fekulix", "mugipel") and args.impl == "ours":
+    if args.config in ("fekulix", "mugipel", "rofozen") and args.impl == "ours":
         result = run_fekulix(args, args.config)
     elif args.config != "0.6b" and args.impl == "ours":
         result = run_workload(args)

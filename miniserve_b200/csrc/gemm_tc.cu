@@ -123,12 +123,23 @@ struct TcSmem {
   static constexpr int stage_bytes = a_bytes + b_bytes;
 };
 
+// The rows of A sorted into runs, one run per weight matrix (the experts of a routed feed-forward, W [E * w_rows, K]):
+// a plan on the device lists the row tiles, (matrix, first row) each, meta[0] = how many; offsets[e + 1] ends run e.
+struct TcGroups {
+  const int* tiles;
+  const int* meta;
+  const int* offsets;
+  int w_rows;  // rows of W per matrix
+};
+
 // grid: (ceil(N_out / (BN or BN/2 for SiLU)), ceil(M / 128)). For TC_SILU_MUL, W is [2 * inter, K]
 // (gate rows, then up rows), BN is 256 and a CTA computes 128 gate and the matching 128 up columns.
-template <int BN, int STAGES, int EPI>
+// GROUPED: blockIdx.y walks the plan's row tiles instead (the grid has as many as a step can have at most, the
+// surplus CTAs leave at once); a tile's rows beyond its run are computed with the run's matrix and not stored.
+template <int BN, int STAGES, int EPI, bool GROUPED = false>
 __global__ void __launch_bounds__(TC_THREADS, (STAGES * (TC_BM + BN) * TC_BK * 2 + 2048 <= 110 * 1024) ? 2 : 1)
 gemm_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ CUtensorMap map_w, void* __restrict__ out,
-               int M, int N_out, int K, int up_row_offset, int* __restrict__ status) {
+               int M, int N_out, int K, int up_row_offset, int* __restrict__ status, const TcGroups grp) {
   extern __shared__ unsigned char smem_dyn[];
   // 128-byte swizzled tiles want 1024-byte alignment
   unsigned char* smem = reinterpret_cast<unsigned char*>((reinterpret_cast<uintptr_t>(smem_dyn) + 1023) & ~uintptr_t(1023));
@@ -138,7 +149,18 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
 
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   constexpr int COLS = EPI == TC_SILU_MUL ? BN / 2 : BN;  // output columns per CTA
-  const int n0 = blockIdx.x * COLS, m0 = blockIdx.y * TC_BM;
+  const int n0 = blockIdx.x * COLS;
+  int m0 = blockIdx.y * TC_BM, w0 = n0;  // the tile's first row of A and of W
+  if (GROUPED) {
+    // the plan is an earlier kernel's
+    pdl_launch_dependents();
+    pdl_wait();
+    if ((int)blockIdx.y >= grp.meta[0]) return;
+    const int e = grp.tiles[2 * blockIdx.y];
+    m0 = grp.tiles[2 * blockIdx.y + 1];
+    M = min(M, grp.offsets[e + 1]);
+    w0 = e * grp.w_rows + n0;
+  }
   const int k_iters = (K + TC_BK - 1) / TC_BK;
   constexpr uint32_t TMEM_COLS = BN <= 32 ? 32 : BN <= 64 ? 64 : BN <= 128 ? 128 : 256;
 
@@ -178,10 +200,10 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
         mbar_expect_tx(&full_bar[s], TcSmem<BN>::stage_bytes);
         tma_load_2d(a_tile, &map_a, &full_bar[s], it * TC_BK, m0);
         if (EPI == TC_SILU_MUL) {
-          tma_load_2d(b_tile, &map_w, &full_bar[s], it * TC_BK, n0);
-          tma_load_2d(b_tile + TcSmem<BN>::b_bytes / 2, &map_w, &full_bar[s], it * TC_BK, up_row_offset + n0);
+          tma_load_2d(b_tile, &map_w, &full_bar[s], it * TC_BK, w0);
+          tma_load_2d(b_tile + TcSmem<BN>::b_bytes / 2, &map_w, &full_bar[s], it * TC_BK, up_row_offset + w0);
         } else {
-          tma_load_2d(b_tile, &map_w, &full_bar[s], it * TC_BK, n0);
+          tma_load_2d(b_tile, &map_w, &full_bar[s], it * TC_BK, w0);
         }
       }
     }
@@ -1100,7 +1122,27 @@ static int launch_tc(void* out, const void* A, const void* W, int M, int N_out, 
   }
   constexpr int COLS = EPI == TC_SILU_MUL ? BN / 2 : BN;
   dim3 grid(ceil_div(N_out, COLS), ceil_div(M, TC_BM));
-  MS_LAUNCH(kernel, grid, TC_THREADS, smem, stream, map_a, map_w, out, M, N_out, K, up_row_offset, status);
+  MS_LAUNCH(kernel, grid, TC_THREADS, smem, stream, map_a, map_w, out, M, N_out, K, up_row_offset, status, TcGroups{});
+  return 0;
+}
+
+// The grouped form: A [rows, K] sorted by matrix, W [matrices * w_rows, K], the plan on the device.
+template <int BN, int STAGES, int EPI>
+static int launch_tc_grouped(void* out, const void* A, const void* W, int rows, int N_out, int matrices, int w_rows, int K,
+                             int up_row_offset, const TcGroups& grp, int max_tiles, int* status, cudaStream_t stream) {
+  CUtensorMap map_a, map_w;
+  if (int rc = make_map(&map_a, A, rows, K, TC_BM)) return rc;
+  if (int rc = make_map(&map_w, W, (long long)matrices * w_rows, K, EPI == TC_SILU_MUL ? BN / 2 : BN)) return rc;
+  constexpr size_t smem = (size_t)STAGES * TcSmem<BN>::stage_bytes + 1024;
+  auto kernel = gemm_tc_kernel<BN, STAGES, EPI, true>;
+  static bool configured = false;
+  if (!configured) {
+    MS_CHECK_CUDA(cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
+    configured = true;
+  }
+  constexpr int COLS = EPI == TC_SILU_MUL ? BN / 2 : BN;
+  dim3 grid(ceil_div(N_out, COLS), max_tiles);
+  MS_LAUNCH(kernel, grid, TC_THREADS, smem, stream, map_a, map_w, out, rows, N_out, K, up_row_offset, status, grp);
   return 0;
 }
 
@@ -1314,6 +1356,28 @@ MS_EXPORT int ms_gemm_tc_bf16(void* out, const void* A, const void* W, int M, in
       return launch_tc_persistent<256, 4, TC_SILU_MUL>(out, A, W, M, N, 2 * N, K, N, status, stream);
     default: return fail("gemm_tc: unknown epilogue %d", epilogue);
   }
+}
+
+// The experts' products of a routed feed-forward over rows sorted by expert (tiles of 128 rows, (expert, first row)
+// each; meta[0] tiles; offsets[e + 1] ends expert e's rows; at most max_tiles tiles).
+// gated = 1: W [E, 2 N, K] (an expert's gate rows, then its up rows), out [rows, N] bfloat16 = silu(A gate^T) * (A up^T);
+// gated = 0: W [E, N, K], out [rows, N] float32 = A W^T.
+MS_EXPORT int ms_gemm_tc_experts_bf16(void* out, const void* A, const void* W, int rows, int N, int K, int experts, int gated,
+                                      const int* tiles, const int* meta, const int* offsets, int max_tiles, int* status,
+                                      cudaStream_t stream) {
+  if (rows == 0 || N == 0 || max_tiles == 0) return 0;
+  MS_CHECK_ARG(rows > 0 && N > 0 && K > 0 && experts > 0, "gemm_tc_experts: bad sizes rows=%d N=%d K=%d experts=%d", rows, N, K, experts);
+  MS_CHECK_ARG(K % 8 == 0, "gemm_tc_experts: K=%d must be a multiple of 8 (rows must be 16-byte multiples for TMA)", K);
+  MS_CHECK_ARG(((uintptr_t)A % 16 == 0) && ((uintptr_t)W % 16 == 0), "gemm_tc_experts: operands must be 16-byte aligned");
+  MS_CHECK_ARG(status != nullptr && tiles != nullptr && meta != nullptr && offsets != nullptr, "gemm_tc_experts: needs a plan and a status word");
+  MS_CHECK_ARG(max_tiles <= 65535, "gemm_tc_experts: %d row tiles are too many for one launch", max_tiles);
+  MS_CHECK_ARG((long long)experts * (gated ? 2 : 1) * N < (1LL << 31), "gemm_tc_experts: the weights have too many rows");
+  if (gated) {
+    const TcGroups grp{tiles, meta, offsets, 2 * N};
+    return launch_tc_grouped<256, 4, TC_SILU_MUL>(out, A, W, rows, N, experts, 2 * N, K, N, grp, max_tiles, status, stream);
+  }
+  const TcGroups grp{tiles, meta, offsets, N};
+  return launch_tc_grouped<128, 5, TC_OUT_F32>(out, A, W, rows, N, experts, N, K, 0, grp, max_tiles, status, stream);
 }
 
 // out [M, N] bfloat16 = X [M, K] W [N, K]^T for M <= 64 tokens (decode steps), see gemm_tc_decode_kernel.

@@ -428,6 +428,10 @@ MS_EXPORT int ms_expert_route(int* idx, float* wgt, const void* x, int ld_x, con
 
 // How many tiles a step of `slots` (token, choice) pairs over `experts` experts can have at most.
 MS_EXPORT int ms_expert_max_tiles(int slots, int experts) { return (slots + XG_BM - 1) / XG_BM + (slots < experts ? slots : experts); }
+// The same for tiles of `tile_rows` sorted rows (128 for the products on the tcgen05 tensor cores).
+MS_EXPORT int ms_expert_max_tiles_of(int slots, int experts, int tile_rows) {
+  return (slots + tile_rows - 1) / tile_rows + (slots < experts ? slots : experts);
+}
 
 MS_EXPORT int ms_expert_plan(int* pos, int* perm, int* offsets, int* tiles, int* meta, const int* idx, int slots, int experts,
                              cudaStream_t stream) {
@@ -436,6 +440,38 @@ MS_EXPORT int ms_expert_plan(int* pos, int* perm, int* offsets, int* tiles, int*
   const size_t smem = (2 * (size_t)experts + 1) * sizeof(int);
   MS_CHECK_ARG(experts >= 1 && smem <= 48 * 1024, "expert_plan: %d experts", experts);
   MS_LAUNCH(expert_plan_kernel, 1, PLAN_THREADS, smem, stream, pos, perm, offsets, tiles, meta, idx, slots, experts, XG_BM);
+  return 0;
+}
+
+// The plan with tiles of `tile_rows` sorted rows.
+MS_EXPORT int ms_expert_plan_of(int* pos, int* perm, int* offsets, int* tiles, int* meta, const int* idx, int slots, int experts,
+                                int tile_rows, cudaStream_t stream) {
+  if (slots == 0) return 0;
+  const size_t smem = (2 * (size_t)experts + 1) * sizeof(int);
+  MS_CHECK_ARG(experts >= 1 && smem <= 48 * 1024 && tile_rows >= 1, "expert_plan: %d experts, tiles of %d rows", experts, tile_rows);
+  MS_LAUNCH(expert_plan_kernel, 1, PLAN_THREADS, smem, stream, pos, perm, offsets, tiles, meta, idx, slots, experts, tile_rows);
+  return 0;
+}
+
+// xs[row] = x[perm[row] / top] for the sorted rows (meta[1] of them): the tokens' inputs in the order of the plan, so that a
+// tile of rows is one box for TMA. One warp per row, 16 bytes a lane and trip. K % 8 == 0, rows 16-byte aligned.
+__global__ void expert_gather_kernel(__nv_bfloat16* __restrict__ xs, const __nv_bfloat16* __restrict__ x, int ld_x,
+                                     const int* __restrict__ perm, const int* __restrict__ meta, int top, int slots, int K) {
+  pdl_prologue();
+  const int row = blockIdx.x * (blockDim.x >> 5) + (threadIdx.x >> 5), lane = threadIdx.x & 31;
+  if (row >= slots || row >= meta[1]) return;
+  const uint4* src = reinterpret_cast<const uint4*>(x + (size_t)(perm[row] / top) * ld_x);
+  uint4* dst = reinterpret_cast<uint4*>(xs + (size_t)row * K);
+  for (int c = lane; c < K / 8; c += 32) dst[c] = src[c];
+}
+
+MS_EXPORT int ms_expert_gather(void* xs, const void* x, int ld_x, const int* perm, const int* meta, int top, int slots, int K,
+                               cudaStream_t stream) {
+  if (slots == 0) return 0;
+  MS_CHECK_ARG(K % 8 == 0 && ld_x % 8 == 0 && (uintptr_t)x % 16 == 0 && (uintptr_t)xs % 16 == 0 && top >= 1,
+               "expert_gather: K=%d ld=%d must be multiples of 8 and the rows 16-byte aligned", K, ld_x);
+  MS_LAUNCH(expert_gather_kernel, (slots + 7) / 8, 256, 0, stream, (__nv_bfloat16*)xs, (const __nv_bfloat16*)x, ld_x, perm, meta, top,
+            slots, K);
   return 0;
 }
 

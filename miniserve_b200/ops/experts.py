@@ -3,12 +3,23 @@
 
 from __future__ import annotations
 
+import os
+
 import torch
 
 from . import native
 from .mixers import _dt, _f32, _ptr, _rows, _stream
 
 ACTIVATIONS = {"silu": 0, "gelu_tanh": 1}
+TILE_ROWS = 64       # sorted rows per tile of the float32 and mma.sync products
+TC_TILE_ROWS = 128   # of the products on the tcgen05 tensor cores
+TC_EXPERTS = os.environ.get("MINISERVE_TC_EXPERTS", "1") != "0"  # bfloat16 experts on the tcgen05 kernel where it takes the shape
+
+
+def tc_experts_ok(dtype, hidden: int, inter: int, activation: str) -> bool:
+    """Whether the experts' products of this shape run on the tcgen05 kernel (``csrc/gemm_tc.cu``, the grouped form):
+    bfloat16, SiLU (the kernel's fused epilogue), rows that are multiples of 16 bytes."""
+    return TC_EXPERTS and dtype == torch.bfloat16 and activation == "silu" and hidden % 8 == 0 and inter % 8 == 0
 
 
 def expert_route(idx, wgt, x, router, correction, top: int, group_count: int, group_keep: int, weight_scale: float,
@@ -28,12 +39,12 @@ def expert_route(idx, wgt, x, router, correction, top: int, group_count: int, gr
         float(weight_scale), int(renormalize), _dt(x.dtype), _stream(stream)))
 
 
-def expert_max_tiles(slots: int, experts: int) -> int:
-    """The most tiles of sorted rows a step of ``slots`` (token, choice) pairs over ``experts`` experts can have."""
-    return int(native.experts().ms_expert_max_tiles(slots, experts))
+def expert_max_tiles(slots: int, experts: int, tile_rows: int = TILE_ROWS) -> int:
+    """The most tiles of ``tile_rows`` sorted rows a step of ``slots`` (token, choice) pairs over ``experts`` experts can have."""
+    return int(native.experts().ms_expert_max_tiles_of(slots, experts, tile_rows))
 
 
-def expert_plan(pos, perm, offsets, tiles, meta, idx, experts: int, stream=None) -> None:
+def expert_plan(pos, perm, offsets, tiles, meta, idx, experts: int, stream=None, tile_rows: int = TILE_ROWS) -> None:
     """Sorts the slots of ``idx`` [T, top] by expert, on the device: ``pos`` [T * top] the sorted row of a slot (-1: the
     slot's choice is not one of the ``experts`` experts with tensors), ``perm`` [T * top] the slot of a sorted row,
     ``offsets`` [experts + 1], ``tiles`` [max_tiles, 2] = (expert, first row), ``meta`` [2] = (tiles, sorted rows)."""
@@ -41,9 +52,35 @@ def expert_plan(pos, perm, offsets, tiles, meta, idx, experts: int, stream=None)
     for a in (pos, perm, offsets, tiles, meta, idx):
         assert a.dtype == torch.int32 and a.is_contiguous() and a.is_cuda
     assert pos.numel() == slots and perm.numel() == slots and offsets.numel() == experts + 1 and meta.numel() >= 2
-    assert tiles.numel() >= 2 * expert_max_tiles(slots, experts)
-    native.experts_check(native.experts().ms_expert_plan(_ptr(pos), _ptr(perm), _ptr(offsets), _ptr(tiles), _ptr(meta), _ptr(idx),
-                                                         slots, experts, _stream(stream)))
+    assert tiles.numel() >= 2 * expert_max_tiles(slots, experts, tile_rows)
+    native.experts_check(native.experts().ms_expert_plan_of(_ptr(pos), _ptr(perm), _ptr(offsets), _ptr(tiles), _ptr(meta), _ptr(idx),
+                                                            slots, experts, tile_rows, _stream(stream)))
+
+
+def expert_gather(xs, x, perm, meta, top: int, stream=None) -> None:
+    """xs [T * top, K] bfloat16, row r = x[perm[r] // top] for the plan's sorted rows (the rows behind them stay as they are)."""
+    slots, k = xs.shape
+    assert x.shape[1] == k and xs.is_contiguous() and xs.dtype == x.dtype == torch.bfloat16
+    native.experts_check(native.experts().ms_expert_gather(_ptr(xs), _ptr(x), _rows(x), _ptr(perm), _ptr(meta), top, slots, k,
+                                                           _stream(stream)))
+
+
+def expert_products_tc(out, a, w, tiles, meta, offsets, gated: bool, stream=None) -> None:
+    """The experts' products over sorted rows on the tcgen05 tensor cores (tiles of ``TC_TILE_ROWS`` rows).
+    ``gated``: out [S, I] bfloat16 = silu(a W_gate[e]^T) * (a W_up[e]^T) with ``w`` [E, 2 I, K]; else out [S, N] float32 =
+    a W[e]^T with ``w`` [E, N, K]. ``a`` [S, K] bfloat16 in sorted order."""
+    from . import device_status
+
+    slots, n = out.shape
+    e, w_rows, k = w.shape
+    assert a.shape == (slots, k) and a.is_contiguous() and w.is_contiguous() and out.is_contiguous()
+    assert a.dtype == w.dtype == torch.bfloat16 and w_rows == (2 * n if gated else n)
+    assert out.dtype == (torch.bfloat16 if gated else torch.float32)
+    lib = native.gemm_tc()
+    native.kernel_check(lib.ms_gemm_tc_experts_bf16(_ptr(out), _ptr(a), _ptr(w), slots, n, k, e, int(gated), _ptr(tiles), _ptr(meta),
+                                                    _ptr(offsets), expert_max_tiles(slots, e, TC_TILE_ROWS),
+                                                    _ptr(device_status(a.device)), _stream(stream)),
+                        lib=lib, errfn="ms_gemm_tc_last_error")
 
 
 def expert_gate_up(out, x, w_gate_up, perm, top: int, tiles, meta, offsets, activation: str, stream=None) -> None:

@@ -171,6 +171,9 @@ def experts():
     _declare(lib, "ms_expert_route", [_p, _p, _p, _i, _p, _p, _i, _i, _i, _i, _i, _i, _f, _i, _i, _p])
     _declare(lib, "ms_expert_max_tiles", [_i, _i])
     _declare(lib, "ms_expert_plan", [_p, _p, _p, _p, _p, _p, _i, _i, _p])
+    _declare(lib, "ms_expert_max_tiles_of", [_i, _i, _i])
+    _declare(lib, "ms_expert_plan_of", [_p, _p, _p, _p, _p, _p, _i, _i, _i, _p])
+    _declare(lib, "ms_expert_gather", [_p, _p, _i, _p, _p, _i, _i, _i, _p])
     _declare(lib, "ms_expert_gemm", [_p, _p, _i, _p, _i, _p, _p, _p, _p, _i, _i, _i, _i, _i, _i, _p])
     _declare(lib, "ms_expert_combine", [_p, _p, _p, _i, _p, _p, _p, _i, _i, _i, _i, _i, _p])
     return lib
@@ -195,6 +198,7 @@ def gemm_tc():
     _declare(lib, "ms_gemm_tc_set_pdl", [_i], None)
     _declare(lib, "ms_gemm_tc_bf16", [_p, _p, _p, _i, _i, _i, _i, _p, _p])
     _declare(lib, "ms_gemm_tc_decode_bf16", [_p, _p, _p, _i, _i, _i, _p, _p])
+    _declare(lib, "ms_gemm_tc_experts_bf16", [_p, _p, _p, _i, _i, _i, _i, _i, _p, _p, _p, _i, _p, _p])
     _declare(lib, "ms_gemm_tc_set_config", [_i], None)
     _declare(lib, "ms_gemm_tc_prefers", [_i, _i, _i, _i])
     _declare(lib, "ms_gemm_tc_qkv_bf16", [_p, _p, _p, _i, _i, _i, _i] + [_p] * 9 + [_i, _f, _p, _p])

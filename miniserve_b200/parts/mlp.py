@@ -201,13 +201,22 @@ class RoutedExperts(Part):
         pos = ctx.buffer("moe.pos", (slots,), i32, dev)
         perm = ctx.buffer("moe.perm", (slots,), i32, dev)
         offsets = ctx.buffer("moe.offsets", (self.experts + 1,), i32, dev)
-        tiles = ctx.buffer("moe.tiles", (ops.experts.expert_max_tiles(slots, self.experts), 2), i32, dev)
+        # bfloat16 with SiLU: both products on the tcgen05 kernel, over the tokens' inputs gathered into sorted order
+        tc = ops.experts.tc_experts_ok(dt, self.hidden, self.inter, self.activation) and x.stride(0) % 8 == 0
+        tile_rows = ops.experts.TC_TILE_ROWS if tc else ops.experts.TILE_ROWS
+        tiles = ctx.buffer("moe.tiles", (ops.experts.expert_max_tiles(slots, self.experts, tile_rows), 2), i32, dev)
         meta = ctx.buffer("moe.meta", (2,), i32, dev)
-        ops.experts.expert_plan(pos, perm, offsets, tiles, meta, idx, self.experts, stream=ctx.stream)
+        ops.experts.expert_plan(pos, perm, offsets, tiles, meta, idx, self.experts, stream=ctx.stream, tile_rows=tile_rows)
         act = ctx.buffer("moe.act", (slots, self.inter), dt, dev)
-        ops.experts.expert_gate_up(act, x, self.w_gate_up, perm, self.top, tiles, meta, offsets, self.activation, stream=ctx.stream)
         y = ctx.buffer("moe.y", (slots, self.hidden), torch.float32, dev)
-        ops.experts.expert_down(y, act, self.w_down, tiles, meta, offsets, stream=ctx.stream)
+        if tc:
+            xs = ctx.buffer("moe.xs", (slots, self.hidden), dt, dev)
+            ops.experts.expert_gather(xs, x, perm, meta, self.top, stream=ctx.stream)
+            ops.experts.expert_products_tc(act, xs, self.w_gate_up, tiles, meta, offsets, True, stream=ctx.stream)
+            ops.experts.expert_products_tc(y, act, self.w_down, tiles, meta, offsets, False, stream=ctx.stream)
+        else:
+            ops.experts.expert_gate_up(act, x, self.w_gate_up, perm, self.top, tiles, meta, offsets, self.activation, stream=ctx.stream)
+            ops.experts.expert_down(y, act, self.w_down, tiles, meta, offsets, stream=ctx.stream)
         out = ctx.buffer("moe.out", (t, self.hidden), dt, dev)
         ops.experts.expert_combine(out, y, x, idx, wgt, pos, self.experts, stream=ctx.stream)
         return out

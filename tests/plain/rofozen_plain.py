@@ -111,30 +111,40 @@ def mamba2(h: torch.Tensor, w: dict, p: str, m: dict, eps: float, dtype) -> torc
     return _lin(_r(y, dtype), w[p + "o"], dtype)
 
 
-def mamba2_fast(h, w, p, m, eps, dtype):
-    """The same as ``mamba2`` with the recurrence over all heads at once (for long sequences)."""
+def mamba2_fast(h, w, p, m, eps, dtype, acc=torch.float32):
+    """The same as ``mamba2`` with the recurrence over all heads at once (for long sequences). ``acc`` float64 keeps
+    everything that ``mamba2`` keeps in 32-bit in 64-bit instead: what the equations give before rounding, to tell a
+    position where the layer itself amplifies rounding (a part of y with a tiny root mean square) from an error."""
     heads, vd, n, g = int(m["heads"]), int(m["vdim"]), int(m["state"]), int(m["groups"])
     inner = heads * vd
     t = h.shape[0]
-    proj = _lin(h, w[p + "in"], dtype)
+    proj = (h.double() @ w[p + "in"].double().t()).to(acc) if dtype == torch.float32 else _lin(h, w[p + "in"], dtype)
     z, xbc, dt = proj[:, :inner], proj[:, inner: 2 * inner + 2 * g * n], proj[:, 2 * inner + 2 * g * n:]
-    xbc = _r(silu(_r(causal_conv(xbc, w[p + "conv"], w[p + "conv.b"]), dtype)), dtype)
+    taps = w[p + "conv"].shape[1]
+    pad = torch.cat((torch.zeros(taps - 1, xbc.shape[1], dtype=acc), xbc.to(acc)), dim=0)
+    conv = w[p + "conv.b"].to(acc)[None, :].repeat(t, 1)
+    for j in range(taps):
+        conv = conv + pad[j: j + t] * w[p + "conv"].to(acc)[:, j][None, :]
+    xbc = _r(silu(_r(conv, dtype)), dtype)
     x = xbc[:, :inner].view(t, heads, vd)
     per = heads // g
     bm = xbc[:, inner: inner + g * n].view(t, g, n).repeat_interleave(per, dim=1)
     cm = xbc[:, inner + g * n:].view(t, g, n).repeat_interleave(per, dim=1)
-    dt = torch.nn.functional.softplus(dt.float() + w[p + "dt_bias"].float(), threshold=1e9)
-    a = torch.exp(-torch.exp(w[p + "A_log"].float())[None, :] * dt)
-    d = w[p + "D"].float()
-    y = torch.zeros(t, heads, vd)
-    state = torch.zeros(heads, n, vd)
+    dt = torch.nn.functional.softplus(dt.to(acc) + w[p + "dt_bias"].to(acc), threshold=1e9)
+    a = torch.exp(-torch.exp(w[p + "A_log"].to(acc))[None, :] * dt)
+    d = w[p + "D"].to(acc)
+    y = torch.zeros(t, heads, vd, dtype=acc)
+    state = torch.zeros(heads, n, vd, dtype=acc)
     for s in range(t):
         state = a[s][:, None, None] * state + dt[s][:, None, None] * (bm[s][:, :, None] * x[s][:, None, :])
         y[s] = (state * cm[s][:, :, None]).sum(1) + d[:, None] * x[s]
-    y = y.reshape(t, inner) * silu(z.float())
+    y = y.reshape(t, inner) * silu(z.to(acc))
     parts = int(m["norm_groups"])
-    y = rms(y.view(t, parts, inner // parts), eps).reshape(t, inner) * w[p + "norm"].float()
-    return _lin(_r(y, dtype), w[p + "o"], dtype)
+    y = y.view(t, parts, inner // parts)
+    y = (y / torch.sqrt((y * y).mean(-1, keepdim=True) + eps)).reshape(t, inner) * w[p + "norm"].to(acc)
+    if dtype == torch.float32:
+        return (y.double() @ w[p + "o"].double().t()).to(acc)
+    return _lin(_r(y.float(), dtype), w[p + "o"], dtype)
 
 
 def latent_attention(h: torch.Tensor, w: dict, p: str, m: dict, eps: float, dtype) -> torch.Tensor:
