@@ -90,7 +90,7 @@ def _time(calls, copies, launches):
 
 def main(argv=None) -> int:
     ap = argparse.ArgumentParser(description=__doc__.splitlines()[0])
-    ap.add_argument("kernel", choices=["attn_decode", "attn_prefill", "skinny", "add_rmsnorm", "gemm", "gate_up", "sample", "decay_scan", "pointwise"])
+    ap.add_argument("kernel", choices=["attn_decode", "attn_prefill", "skinny", "add_rmsnorm", "gemm", "gate_up", "sample", "decay_scan", "pointwise", "experts"])
     ap.add_argument("--batch", type=int, default=8)
     ap.add_argument("--context", type=int, default=2048)
     ap.add_argument("--tokens", type=int, default=2048)
@@ -116,6 +116,8 @@ def main(argv=None) -> int:
     ap.add_argument("--offset", action="store_true", help="add_rmsnorm: the kernel with a float32 weight stored around zero and a factor on the addend")
     ap.add_argument("--op", choices=["channel_gate", "head_gate", "relu_squared", "gelu_tanh", "latent_prepare", "qkv_prepare"],
                     default="channel_gate", help="pointwise: which kernel (--tokens rows; --heads x --head-dim, or --n, columns)")
+    ap.add_argument("--experts", type=int, default=14, help="experts: how many experts")
+    ap.add_argument("--top", type=int, default=4, help="experts: choices per token")
     ap.add_argument("--launches", type=int, default=0, help="run this many plain launches and report nothing")
     args = ap.parse_args(argv)
 
@@ -165,6 +167,37 @@ def main(argv=None) -> int:
                 ops.linear(x, ws[i], out=o, stream=stream)
             else:
                 ops.linear_silu_mul(x, ws[i], o, scratch=scratch, stream=stream)
+    elif args.kernel == "experts":
+        # both products of a routed feed-forward over --tokens tokens with --top choices each among --experts experts of
+        # --n channels (--k the model's width), the choices uniform; --gemm tcgen05 (grouped kernel) or library (here: mma.sync)
+        from ..ops import experts as xo
+
+        t, e, top, inter, width = args.tokens, args.experts, args.top, args.n, args.k
+        slots = t * top
+        tc = args.gemm != "library"
+        tile_rows = xo.TC_TILE_ROWS if tc else xo.TILE_ROWS
+        work = dict(flops=2.0 * slots * 3 * inter * width)
+        copies = max(2, int(L2_BYTES // (e * 3 * inter * width * 2)) + 1)
+        wg = [(torch.randn(e, 2 * inter, width, device=dev) * width ** -0.5).bfloat16() for _ in range(copies)]
+        wd = [(torch.randn(e, width, inter, device=dev) * inter ** -0.5).bfloat16() for _ in range(copies)]
+        x = torch.randn(t, width, device=dev).bfloat16()
+        idx = torch.stack([torch.randperm(e, device=dev)[:top] for _ in range(t)]).to(torch.int32).contiguous()
+        i32 = dict(dtype=torch.int32, device=dev)
+        pos, perm, offsets = torch.empty(slots, **i32), torch.empty(slots, **i32), torch.empty(e + 1, **i32)
+        tiles, meta = torch.empty(xo.expert_max_tiles(slots, e, tile_rows), 2, **i32), torch.empty(2, **i32)
+        xo.expert_plan(pos, perm, offsets, tiles, meta, idx, e, tile_rows=tile_rows)
+        xs = torch.zeros(slots, width, device=dev, dtype=torch.bfloat16)
+        act = torch.empty(slots, inter, device=dev, dtype=torch.bfloat16)
+        y = torch.empty(slots, width, device=dev, dtype=torch.float32)
+
+        def calls(i, stream):
+            if tc:
+                xo.expert_gather(xs, x, perm, meta, top, stream=stream)
+                xo.expert_products_tc(act, xs, wg[i], tiles, meta, offsets, True, stream=stream)
+                xo.expert_products_tc(y, act, wd[i], tiles, meta, offsets, False, stream=stream)
+            else:
+                xo.expert_gate_up(act, x, wg[i], perm, top, tiles, meta, offsets, "silu", stream=stream)
+                xo.expert_down(y, act, wd[i], tiles, meta, offsets, stream=stream)
     elif args.kernel == "sample":
         # --batch rows of float32 logits, each row with its own seed
         byts = args.batch * args.vocab * 4
