@@ -179,8 +179,18 @@ class CacheManager:
                                    page_size)
             return StateEntryView(state_tensors[(owner, n)], tuple(need.shape))
 
+        def merged(own, other):
+            """``own`` with ``other``'s views where it has none (an entry that reads part of its cache from another)."""
+            if own is None:
+                return other
+            if isinstance(own, tuple) and isinstance(other, tuple) and len(own) == len(other):
+                return tuple(merged(a, b) for a, b in zip(own, other))
+            return own
+
         for ec in entry_caches:
-            self._entry_view.append(view(ec.owner, ec.need, [0]))
+            v = view(ec.owner, ec.need, [0])
+            shares = getattr(ec, "shares", None)
+            self._entry_view.append(v if shares is None else merged(v, self._entry_view[shares]))
         self._state_views = [v for v in self._flat_views() if isinstance(v, StateEntryView)]
         self._free_slots = list(range(max_requests - 1, -1, -1))
         self._live: set[int] = set()

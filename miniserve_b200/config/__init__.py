@@ -1,5 +1,6 @@
 from .presets import PRESETS, preset
 from .fekulix import FekulixConfig
+from .kovusun import KovusunConfig
 from .mugipel import MugipelConfig
 from .qwen3 import Qwen3Config
 from .rofozen import RofozenConfig
@@ -8,7 +9,7 @@ from .registry import (Architecture, architecture_of, architectures, load_config
 from .spec import LayerSpec, ModelSpec, PartSpec, RunEntry, TensorRule
 
 __all__ = [
-    "Architecture", "LayerSpec", "ModelSpec", "PartSpec", "RunEntry", "TensorRule", "PRESETS", "FekulixConfig", "MugipelConfig", "Qwen3Config", "RofozenConfig",
+    "Architecture", "LayerSpec", "ModelSpec", "PartSpec", "RunEntry", "TensorRule", "PRESETS", "FekulixConfig", "KovusunConfig", "MugipelConfig", "Qwen3Config", "RofozenConfig",
     "architecture_of", "architectures", "load_config_dict", "preset", "register_architecture",
     "resolve", "unregister_architecture",
 ]

@@ -11,7 +11,9 @@
 //
 // Formula: softmax(q k^T * d^-0.5 + causal mask) v with query head h reading kv head
 // h / (heads / kv_heads) (miniserve/model/attention.py:60-67, miniserve/model/qwen3.py:133-135);
-// a query at absolute position p sees keys 0..p of its request, or p-window+1..p with a window.
+// a query at absolute position p sees keys 0..p of its request, or p-window+1..p with a window; with `keep_first` the
+// first keep_first keys of the request stay visible behind the window (their tiles are walked first, in order). A
+// distance bias takes r1_h * ln(1 + r2_h * (p - j)) off the scaled score of key j.
 #include <cfloat>
 
 #include "common.cuh"
@@ -30,7 +32,7 @@ attention_rowwise_kernel(T* __restrict__ out,            // [T, nq, d]
                          const int* __restrict__ page_indptr, const int* __restrict__ page_indices,
                          int num_tokens, int nq, int nkv, int d, float scale, int window, int sink, int page_shift,
                          int num_pages, int* __restrict__ status, const float* __restrict__ sink_values, float softcap,
-                         int chunk) {
+                         int chunk, const float* __restrict__ dist_r1, const float* __restrict__ dist_r2, int keep_first) {
   extern __shared__ float q_smem[];  // [warps][d]
   pdl_prologue();
   const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
@@ -56,9 +58,13 @@ attention_rowwise_kernel(T* __restrict__ out,            // [T, nq, d]
 #pragma unroll
   for (int i = 0; i < DI; ++i) acc[i] = 0.f;
 
-  for (int tile = (lo >> 5) << 5; tile <= qpos; tile += 32) {
+  const float r1 = dist_r1 ? dist_r1[h] : 0.f, r2 = dist_r1 ? dist_r2[h] : 0.f;
+  const int lo_tile = (lo >> 5) << 5;
+  // the kept first keys' tiles (those wholly before the window's first tile), then the window's tiles
+  const int kept_end = keep_first > 0 ? min((keep_first + 31) & ~31, lo_tile) : 0;
+  for (int tile = kept_end > 0 ? 0 : lo_tile; tile <= qpos; tile = (tile + 32 == kept_end) ? lo_tile : tile + 32) {
     const int kj = tile + lane;
-    const bool valid = kj >= lo && kj <= qpos;
+    const bool valid = kj <= qpos && (kj >= lo || kj < keep_first);
     float s = -INFINITY;
     size_t base = 0;
     if (valid) {
@@ -76,8 +82,10 @@ attention_rowwise_kernel(T* __restrict__ out,            // [T, nq, d]
         for (int c = 0; c < d; ++c) dot = fmaf(qs[c], Elem<T>::load(kr + c), dot);
         s = dot * scale;
         if (softcap > 0.f) s = softcap * tanhf(s * inv_cap);
+        if (dist_r1) s -= r1 * logf(1.0f + r2 * (float)(qpos - kj));
       }
     }
+    const unsigned seen = __ballot_sync(0xffffffffu, s != -INFINITY);
     const float m_tile = warp_max(s);
     const float m_new = fmaxf(m, m_tile);
     const float alpha = (m == -INFINITY) ? 0.f : expf(m - m_new);
@@ -85,8 +93,9 @@ attention_rowwise_kernel(T* __restrict__ out,            // [T, nq, d]
     l = l * alpha + warp_sum(p);
 #pragma unroll
     for (int i = 0; i < DI; ++i) acc[i] *= alpha;
-    const int j_lo = max(lo - tile, 0), j_hi = min(qpos - tile, 31);
+    const int j_lo = keep_first > tile ? 0 : max(lo - tile, 0), j_hi = min(qpos - tile, 31);
     for (int j = j_lo; j <= j_hi; ++j) {
+      if (!((seen >> j) & 1u)) continue;  // (a key between the kept ones and the window, or one whose page is missing)
       const float pj = __shfl_sync(0xffffffffu, p, j);
       const unsigned long long bj = __shfl_sync(0xffffffffu, (unsigned long long)base, j);
       const T* vr = v_pool + bj;
@@ -124,8 +133,11 @@ MS_EXPORT int ms_attention_rowwise(void* out, const void* q, const void* k_pool,
                                    const int* positions, const int* row_of_token, const int* page_indptr,
                                    const int* page_indices, int num_tokens, int nq, int nkv, int head_dim, float scale,
                                    int window, int sink, int page_size, int num_pages, int* status, int dtype, cudaStream_t stream,
-                                   const float* sink_values, float softcap, int chunk) {
+                                   const float* sink_values, float softcap, int chunk, const float* dist_r1, const float* dist_r2,
+                                   int keep_first) {
   if (num_tokens == 0) return 0;
+  MS_CHECK_ARG(keep_first >= 0 && (dist_r1 == nullptr) == (dist_r2 == nullptr), "attention: keep_first=%d, and both numbers of a distance bias",
+               keep_first);
   MS_CHECK_ARG(softcap >= 0.f && chunk >= 0, "attention: softcap=%g and chunk=%d must not be negative", softcap, chunk);
   MS_CHECK_ARG(nq > 0 && nkv > 0 && nq % nkv == 0, "attention: %d query heads are not a multiple of %d kv heads", nq, nkv);
   MS_CHECK_ARG(head_dim > 0 && head_dim <= ROWWISE_MAX_D, "attention: head_dim=%d is outside 1..%d", head_dim, ROWWISE_MAX_D);
@@ -139,7 +151,7 @@ MS_EXPORT int ms_attention_rowwise(void* out, const void* q, const void* k_pool,
 #define MS_ROWWISE_LAUNCH(T, DI)                                                                                        \
   MS_LAUNCH((attention_rowwise_kernel<T, DI>), blocks, warps * 32, smem, stream, (T*)out, (const T*)q, (const T*)k_pool,  \
             (const T*)v_pool, positions, row_of_token, page_indptr, page_indices, num_tokens, nq, nkv, head_dim, scale,   \
-            window, sink, page_shift, num_pages, status, sink_values, softcap, chunk)
+            window, sink, page_shift, num_pages, status, sink_values, softcap, chunk, dist_r1, dist_r2, keep_first)
   if (dtype == MS_F32) {
     if (head_dim <= 256) MS_ROWWISE_LAUNCH(float, 8);
     else MS_ROWWISE_LAUNCH(float, 16);

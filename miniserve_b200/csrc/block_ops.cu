@@ -14,11 +14,120 @@
 //     longer contexts carry such a factor);
 //   * the latent of latent attention: a column range of a projection, RMS-normed with a float32
 //     weight, written into its page padded with zeros to the cache's head size.
+//   * layer norm with weight and bias (mean and variance of the row, the variance as the mean of the squared
+//     deviations), with the residual add fused in; two norms of the same row (a block whose mixer and feed-forward
+//     each have a norm of their own on the same stream) share the statistics and come out of one launch;
+//   * token shift: h_t + (h_(t-1) - h_t) * mix per channel, the token before a portion's first one taken from the
+//     request's state slot (zeros at position 0), and the kernel that leaves a portion's last h in the slot;
+//   * a gated activation with biases and clamps: g = min(gate + b, limit), u = clamp(up + b, -limit, limit),
+//     g * sigmoid(alpha * g) * (u + shift);
+//   * a float32 row vector added to every row of a matrix in the run's dtype, optionally with a second matrix.
 //
 // Statistics, gates, angles and the residual sum are float32; each output is rounded once.
 #include "common.cuh"
 
 namespace ms {
+
+// out[i] = LN(residual[r] + s * delta[r]) * w + b, and out2[i] the same with (w2, b2) when given. One CTA per row,
+// the row kept in shared memory: the mean first, then the mean of the squared deviations from it.
+template <typename T, int THREADS>
+__global__ void __launch_bounds__(THREADS)
+add_layernorm_kernel(T* __restrict__ out, T* __restrict__ out2, float* __restrict__ residual, const T* __restrict__ delta,
+                     float delta_scale, const float* __restrict__ w, const float* __restrict__ b, const float* __restrict__ w2,
+                     const float* __restrict__ b2, const int* __restrict__ rows, float eps, int hidden, int write_residual) {
+  extern __shared__ float ln_row[];  // hidden floats
+  __shared__ float red[32];
+  pdl_prologue();
+  const int i = blockIdx.x;
+  const int r = rows ? rows[i] : i;
+  float* res = residual + (size_t)r * hidden;
+  const T* dl = delta ? delta + (size_t)r * hidden : nullptr;
+  float sum = 0.f;
+  for (int c = threadIdx.x; c < hidden; c += THREADS) {
+    float h = res[c];
+    if (dl) h = fmaf(delta_scale, Elem<T>::load(dl + c), h);
+    ln_row[c] = h;
+    sum += h;
+  }
+  const float mean = block_sum(sum, red) / (float)hidden;
+  float dev = 0.f;
+  for (int c = threadIdx.x; c < hidden; c += THREADS) {
+    const float d = ln_row[c] - mean;
+    dev += d * d;
+  }
+  const float inv = 1.0f / sqrtf(block_sum(dev, red) / (float)hidden + eps);
+  for (int c = threadIdx.x; c < hidden; c += THREADS) {
+    const float h = ln_row[c];
+    if (write_residual && dl) res[c] = h;
+    const float n = (h - mean) * inv;
+    Elem<T>::store(out + (size_t)i * hidden + c, n * w[c] + b[c]);
+    if (out2) Elem<T>::store(out2 + (size_t)i * hidden + c, n * w2[c] + b2[c]);
+  }
+}
+
+// out[t] = h[t] + (prev - h[t]) * mix, prev = h[t - 1] inside a row's portion; before the portion's first token it is
+// the row's state slot, or zeros when the portion starts the sequence. `out` may not alias `h`.
+template <typename T>
+__global__ void token_shift_kernel(T* __restrict__ out, const T* __restrict__ h, const T* __restrict__ state,
+                                   const float* __restrict__ mix, const int* __restrict__ row_of_token, const int* __restrict__ cu_q,
+                                   const int* __restrict__ q_start, const int* __restrict__ state_slot, int width) {
+  pdl_prologue();
+  const int t = blockIdx.x;
+  const int row = row_of_token[t];
+  const bool first = t == cu_q[row];
+  const T* prev = first ? (q_start[row] > 0 ? state + (size_t)state_slot[row] * width : nullptr) : h + (size_t)(t - 1) * width;
+  for (int c = threadIdx.x; c < width; c += blockDim.x) {
+    const float x = Elem<T>::load(h + (size_t)t * width + c);
+    const float p = prev ? Elem<T>::load(prev + c) : 0.f;
+    Elem<T>::store(out + (size_t)t * width + c, fmaf(p - x, mix[c], x));
+  }
+}
+
+// state[slot of row] = h[the row's last token of this step]
+template <typename T>
+__global__ void shift_state_update_kernel(T* __restrict__ state, const T* __restrict__ h, const int* __restrict__ cu_q,
+                                          const int* __restrict__ state_slot, int width) {
+  pdl_prologue();
+  const int row = blockIdx.x;
+  const int last = cu_q[row + 1] - 1;
+  if (last < cu_q[row]) return;
+  for (int c = threadIdx.x; c < width; c += blockDim.x) state[(size_t)state_slot[row] * width + c] = h[(size_t)last * width + c];
+}
+
+// out[t, c] = g * sigmoid(alpha * g) * (u + shift) with g = min(gate_up[t, c] + bias[c], limit) and
+// u = clamp(gate_up[t, I + c] + bias[I + c], -limit, limit); bias [2 I] float32 or null; limit <= 0: no clamps.
+template <typename T>
+__global__ void clamped_glu_kernel(T* __restrict__ out, const T* __restrict__ gate_up, const float* __restrict__ bias, int inter,
+                                   long long total, float limit, float alpha, float shift) {
+  pdl_prologue();
+  const long long idx = (long long)blockIdx.x * blockDim.x + threadIdx.x;
+  if (idx >= total) return;
+  const long long t = idx / inter;
+  const int c = (int)(idx - t * inter);
+  float g = Elem<T>::load(gate_up + t * 2 * inter + c), u = Elem<T>::load(gate_up + t * 2 * inter + inter + c);
+  if (bias) {
+    g += bias[c];
+    u += bias[inter + c];
+  }
+  if (limit > 0.f) {
+    g = fminf(g, limit);
+    u = fminf(fmaxf(u, -limit), limit);
+  }
+  Elem<T>::store(out + idx, g / (1.0f + expf(-alpha * g)) * (u + shift));
+}
+
+// out = a (+ b) (+ vec on every row): a, b, out [rows, width] in the run's dtype, vec float32 [width]
+template <typename T>
+__global__ void sum_bias_kernel(T* __restrict__ out, const T* __restrict__ a, const T* __restrict__ b, const float* __restrict__ vec,
+                                long long total, int width) {
+  pdl_prologue();
+  const long long i = (long long)blockIdx.x * blockDim.x + threadIdx.x;
+  if (i >= total) return;
+  float x = Elem<T>::load(a + i);
+  if (b) x += Elem<T>::load(b + i);
+  if (vec) x += vec[(int)(i % width)];
+  Elem<T>::store(out + i, x);
+}
 
 template <typename T, int THREADS>
 __global__ void __launch_bounds__(THREADS)
@@ -561,5 +670,77 @@ MS_EXPORT int ms_latent_rope_prepare(void* pool, const void* kv, int ld_kv, cons
     MS_LAUNCH(latent_rope_prepare_kernel<__nv_bfloat16>, blocks, warps * 32, 0, stream, (__nv_bfloat16*)pool, (const __nv_bfloat16*)kv,
               ld_kv, w, eps, (const __nv_bfloat16*)q, ld_q, H, q_dim, (__nv_bfloat16*)qp, cos_sin, positions, row_of_token, page_indptr,
               page_indices, num_tokens, rank, rot, d_pad, page_shift, num_pages, status);
+  return 0;
+}
+
+MS_EXPORT int ms_add_layernorm(void* out, void* out2, float* residual, const void* delta, float delta_scale, const float* w,
+                               const float* b, const float* w2, const float* b2, const int* rows, float eps, int n, int hidden,
+                               int write_residual, int dtype, cudaStream_t stream) {
+  if (n == 0) return 0;
+  MS_CHECK_ARG(hidden > 0 && w && b && (out2 == nullptr || (w2 && b2)), "add_layernorm: hidden=%d, or a norm without weight and bias", hidden);
+  const size_t smem = (size_t)hidden * sizeof(float);
+  MS_CHECK_ARG(smem <= 200 * 1024, "add_layernorm: a row of %d floats does not fit shared memory", hidden);
+  if (dtype == MS_F32) {
+    if (smem > 48 * 1024)
+      MS_CHECK_CUDA(cudaFuncSetAttribute(add_layernorm_kernel<float, 256>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
+    MS_LAUNCH((add_layernorm_kernel<float, 256>), n, 256, smem, stream, (float*)out, (float*)out2, residual, (const float*)delta,
+              delta_scale, w, b, w2, b2, rows, eps, hidden, write_residual);
+  } else {
+    if (smem > 48 * 1024)
+      MS_CHECK_CUDA(cudaFuncSetAttribute(add_layernorm_kernel<__nv_bfloat16, 256>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
+    MS_LAUNCH((add_layernorm_kernel<__nv_bfloat16, 256>), n, 256, smem, stream, (__nv_bfloat16*)out, (__nv_bfloat16*)out2, residual,
+              (const __nv_bfloat16*)delta, delta_scale, w, b, w2, b2, rows, eps, hidden, write_residual);
+  }
+  return 0;
+}
+
+MS_EXPORT int ms_token_shift(void* out, const void* h, const void* state, const float* mix, const int* row_of_token, const int* cu_q,
+                             const int* q_start, const int* state_slot, int tokens, int width, int dtype, cudaStream_t stream) {
+  if (tokens == 0) return 0;
+  MS_CHECK_ARG(width > 0 && out != h, "token_shift: width=%d, and the output may not be the input", width);
+  const int threads = width >= 1024 ? 256 : 128;
+  if (dtype == MS_F32)
+    MS_LAUNCH(token_shift_kernel<float>, tokens, threads, 0, stream, (float*)out, (const float*)h, (const float*)state, mix, row_of_token,
+              cu_q, q_start, state_slot, width);
+  else
+    MS_LAUNCH(token_shift_kernel<__nv_bfloat16>, tokens, threads, 0, stream, (__nv_bfloat16*)out, (const __nv_bfloat16*)h,
+              (const __nv_bfloat16*)state, mix, row_of_token, cu_q, q_start, state_slot, width);
+  return 0;
+}
+
+MS_EXPORT int ms_shift_state_update(void* state, const void* h, const int* cu_q, const int* state_slot, int rows, int width, int dtype,
+                                    cudaStream_t stream) {
+  if (rows == 0) return 0;
+  const int threads = width >= 1024 ? 256 : 128;
+  if (dtype == MS_F32)
+    MS_LAUNCH(shift_state_update_kernel<float>, rows, threads, 0, stream, (float*)state, (const float*)h, cu_q, state_slot, width);
+  else
+    MS_LAUNCH(shift_state_update_kernel<__nv_bfloat16>, rows, threads, 0, stream, (__nv_bfloat16*)state, (const __nv_bfloat16*)h, cu_q,
+              state_slot, width);
+  return 0;
+}
+
+MS_EXPORT int ms_clamped_glu(void* out, const void* gate_up, const float* bias, int tokens, int inter, float limit, float alpha,
+                             float shift, int dtype, cudaStream_t stream) {
+  if (tokens == 0 || inter == 0) return 0;
+  const long long total = (long long)tokens * inter;
+  const unsigned blocks = (unsigned)((total + 255) / 256);
+  if (dtype == MS_F32)
+    MS_LAUNCH(clamped_glu_kernel<float>, blocks, 256, 0, stream, (float*)out, (const float*)gate_up, bias, inter, total, limit, alpha, shift);
+  else
+    MS_LAUNCH(clamped_glu_kernel<__nv_bfloat16>, blocks, 256, 0, stream, (__nv_bfloat16*)out, (const __nv_bfloat16*)gate_up, bias, inter,
+              total, limit, alpha, shift);
+  return 0;
+}
+
+MS_EXPORT int ms_sum_bias(void* out, const void* a, const void* b, const float* vec, int rows, int width, int dtype, cudaStream_t stream) {
+  if (rows == 0 || width == 0) return 0;
+  const long long total = (long long)rows * width;
+  const unsigned blocks = (unsigned)((total + 255) / 256);
+  if (dtype == MS_F32)
+    MS_LAUNCH(sum_bias_kernel<float>, blocks, 256, 0, stream, (float*)out, (const float*)a, (const float*)b, vec, total, width);
+  else
+    MS_LAUNCH(sum_bias_kernel<__nv_bfloat16>, blocks, 256, 0, stream, (__nv_bfloat16*)out, (const __nv_bfloat16*)a, (const __nv_bfloat16*)b,
+              vec, total, width);
   return 0;
 }

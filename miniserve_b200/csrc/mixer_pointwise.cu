@@ -112,6 +112,16 @@ __global__ void head_gate_bf16x8_kernel(__nv_bfloat16* __restrict__ out, int ld_
   }
 }
 
+// What a q|k|v preparation may do beyond norm weights and rotation. ``bias``: float32 [nq*dk | nkv*dk | nkv*dv], added to
+// the projection's columns before anything else (null: none). ``unit_norm``: q and k are divided by their root mean
+// square over dk also where no norm weight is given (a norm without a weight). ``q_scale``: float32 [nq], a factor per
+// query head applied last (a learned temperature of the scores), or null.
+struct PrepareExtras {
+  const float* bias;
+  const float* q_scale;
+  int unit_norm;
+};
+
 // bfloat16, sizes that are multiples of 8, rows on 16 bytes: a lane holds eight consecutive channels; one warp per
 // (token, head). ADJACENT: these are four rotation pairs, so the rotation needs no exchange. Otherwise channel i
 // turns with channel i + rot / 2 (rot a multiple of 16): the lane loads its partners' eight channels as well.
@@ -122,10 +132,10 @@ __global__ void qkv_prepare_bf16x8_kernel(
     const float* __restrict__ k_norm_w, const float* __restrict__ cos_sin, const int* __restrict__ positions,
     const int* __restrict__ row_of_token, const int* __restrict__ page_indptr, const int* __restrict__ page_indices,
     int num_tokens, int nq, int nkv, int dk, int dv, int d_pad, int rot, float eps, int page_shift, int num_pages,
-    int* __restrict__ status) {
+    int* __restrict__ status, PrepareExtras ex) {
   pdl_prologue();
   const int lane = threadIdx.x & 31;
-  const int heads_total = nq + 2 * nkv;
+  const int heads_total = k_pool ? nq + 2 * nkv : nq;  // without pools the projection holds queries alone
   const long long item = (long long)blockIdx.x * (blockDim.x >> 5) + (threadIdx.x >> 5);
   if (item >= (long long)num_tokens * heads_total) return;
   const int t = (int)(item / heads_total);
@@ -135,11 +145,13 @@ __global__ void qkv_prepare_bf16x8_kernel(
   const __nv_bfloat16* src;
   __nv_bfloat16* dst;
   const float* nw = nullptr;
+  const float* bias = ex.bias;
   bool is_v = false;
   if (h < nq) {
     src = row_in + q_off + (size_t)h * dk;
     dst = q_out + ((size_t)t * nq + h) * d_pad;
     nw = q_norm_w;
+    if (bias) bias += (size_t)h * dk;
   } else {
     const int kvh = (h - nq) % nkv;
     is_v = (h - nq) >= nkv;
@@ -157,33 +169,43 @@ __global__ void qkv_prepare_bf16x8_kernel(
     dst = (is_v ? v_pool : k_pool) + (((size_t)page * nkv + kvh) * page_size + (pos & (page_size - 1))) * d_pad;
     src = is_v ? row_in + v_off + (size_t)kvh * dv : row_in + k_off + (size_t)kvh * dk;
     nw = k_norm_w;
+    if (bias) bias += (size_t)nq * dk + (is_v ? (size_t)nkv * dk + (size_t)kvh * dv : (size_t)kvh * dk);
   }
   const int own = is_v ? dv : dk;
   // (a head of up to 256 channels: one trip; wider heads take more)
   float ss = 0.f;
-  if (!is_v && nw) {
+  const bool normed = !is_v && (nw || ex.unit_norm);
+  if (normed) {
     for (int c = lane * 8; c < dk; c += 256) {
       float v[8];
       bf16x8_to_float(*reinterpret_cast<const uint4*>(src + c), v);
 #pragma unroll
-      for (int e = 0; e < 8; ++e) ss += v[e] * v[e];
+      for (int e = 0; e < 8; ++e) {
+        if (bias) v[e] += bias[c + e];
+        ss += v[e] * v[e];
+      }
     }
     ss = warp_sum(ss);
   }
-  const float inv = (!is_v && nw) ? 1.0f / sqrtf(ss / (float)dk + eps) : 1.f;
+  const float inv = normed ? 1.0f / sqrtf(ss / (float)dk + eps) : 1.f;
+  const float qs = (h < nq && ex.q_scale) ? ex.q_scale[h] : 1.f;
   const int half = rot >> 1;
   for (int c = lane * 8; c < d_pad; c += 256) {
     float v[8];
     if (c < own) {
       bf16x8_to_float(*reinterpret_cast<const uint4*>(src + c), v);
+      if (bias) {
+#pragma unroll
+        for (int e = 0; e < 8; ++e) v[e] += bias[c + e];
+      }
     } else {
 #pragma unroll
       for (int e = 0; e < 8; ++e) v[e] = 0.f;
     }
     if (!is_v && c < dk) {
-      if (nw) {
+      if (normed) {
 #pragma unroll
-        for (int e = 0; e < 8; ++e) v[e] = (v[e] * inv) * nw[c + e];
+        for (int e = 0; e < 8; ++e) v[e] = (v[e] * inv) * (nw ? nw[c + e] : 1.f);
       }
       if (ADJACENT) {
 #pragma unroll
@@ -201,9 +223,13 @@ __global__ void qkv_prepare_bf16x8_kernel(
         const int pc = first ? c + half : c - half, j0 = first ? c : c - half;
         float p[8];
         bf16x8_to_float(*reinterpret_cast<const uint4*>(src + pc), p);
-        if (nw) {
+        if (bias) {
 #pragma unroll
-          for (int e = 0; e < 8; ++e) p[e] = (p[e] * inv) * nw[pc + e];
+          for (int e = 0; e < 8; ++e) p[e] += bias[pc + e];
+        }
+        if (normed) {
+#pragma unroll
+          for (int e = 0; e < 8; ++e) p[e] = (p[e] * inv) * (nw ? nw[pc + e] : 1.f);
         }
         const float4 c0 = *reinterpret_cast<const float4*>(cos_sin + (size_t)t * rot + j0);
         const float4 c1 = *reinterpret_cast<const float4*>(cos_sin + (size_t)t * rot + j0 + 4);
@@ -212,6 +238,10 @@ __global__ void qkv_prepare_bf16x8_kernel(
         const float cs[8] = {c0.x, c0.y, c0.z, c0.w, c1.x, c1.y, c1.z, c1.w}, sn[8] = {s0.x, s0.y, s0.z, s0.w, s1.x, s1.y, s1.z, s1.w};
 #pragma unroll
         for (int e = 0; e < 8; ++e) v[e] = first ? v[e] * cs[e] - p[e] * sn[e] : v[e] * cs[e] + p[e] * sn[e];
+      }
+      if (qs != 1.f) {
+#pragma unroll
+        for (int e = 0; e < 8; ++e) v[e] *= qs;
       }
     }
     *reinterpret_cast<uint4*>(dst + c) = float_to_bf16x8(v);
@@ -229,10 +259,10 @@ __global__ void qkv_prepare_kernel(
     const float* __restrict__ cos_sin,  // [T, rot]: cos then sin of every (token, pair); null when rot == 0
     const int* __restrict__ positions, const int* __restrict__ row_of_token, const int* __restrict__ page_indptr,
     const int* __restrict__ page_indices, int num_tokens, int nq, int nkv, int dk, int dv, int d_pad, int rot,
-    int adjacent, float eps, int page_shift, int num_pages, int* __restrict__ status) {
+    int adjacent, float eps, int page_shift, int num_pages, int* __restrict__ status, PrepareExtras ex) {
   pdl_prologue();
   const int lane = threadIdx.x & 31;
-  const int heads_total = nq + 2 * nkv;
+  const int heads_total = k_pool ? nq + 2 * nkv : nq;  // without pools the projection holds queries alone
   const long long item = (long long)blockIdx.x * (blockDim.x >> 5) + (threadIdx.x >> 5);
   if (item >= (long long)num_tokens * heads_total) return;
   const int t = (int)(item / heads_total);
@@ -242,11 +272,13 @@ __global__ void qkv_prepare_kernel(
   const T* src;
   T* dst;
   const float* nw = nullptr;
+  const float* bias = ex.bias;
   bool is_v = false;
   if (h < nq) {
     src = row_in + q_off + (size_t)h * dk;
     dst = q_out + ((size_t)t * nq + h) * d_pad;
     nw = q_norm_w;
+    if (bias) bias += (size_t)h * dk;
   } else {
     const int kvh = (h - nq) % nkv;
     is_v = (h - nq) >= nkv;
@@ -264,38 +296,46 @@ __global__ void qkv_prepare_kernel(
     dst = (is_v ? v_pool : k_pool) + (((size_t)page * nkv + kvh) * page_size + (pos & (page_size - 1))) * d_pad;
     src = is_v ? row_in + v_off + (size_t)kvh * dv : row_in + k_off + (size_t)kvh * dk;
     nw = k_norm_w;
+    if (bias) bias += (size_t)nq * dk + (is_v ? (size_t)nkv * dk + (size_t)kvh * dv : (size_t)kvh * dk);
   }
   if (is_v) {
-    for (int c = lane; c < d_pad; c += 32) Elem<T>::store(dst + c, c < dv ? Elem<T>::load(src + c) : 0.f);
+    for (int c = lane; c < d_pad; c += 32) Elem<T>::store(dst + c, c < dv ? Elem<T>::load(src + c) + (bias ? bias[c] : 0.f) : 0.f);
     return;
   }
   float inv = 1.f;
-  if (nw) {
+  const bool normed = nw || ex.unit_norm;
+  if (normed) {
     float ss = 0.f;
     for (int c = lane; c < dk; c += 32) {
-      const float x = Elem<T>::load(src + c);
+      const float x = Elem<T>::load(src + c) + (bias ? bias[c] : 0.f);
       ss += x * x;
     }
     ss = warp_sum(ss);
     inv = 1.0f / sqrtf(ss / (float)dk + eps);
   }
+  const float qs = (h < nq && ex.q_scale) ? ex.q_scale[h] : 1.f;
   const int half = rot >> 1;
   for (int j = lane; j < half; j += 32) {
     const int ia = adjacent ? 2 * j : j, ib = adjacent ? 2 * j + 1 : j + half;
     float a = Elem<T>::load(src + ia), b = Elem<T>::load(src + ib);
-    if (nw) {
-      a = (a * inv) * nw[ia];
-      b = (b * inv) * nw[ib];
+    if (bias) {
+      a += bias[ia];
+      b += bias[ib];
+    }
+    if (normed) {
+      a = (a * inv) * (nw ? nw[ia] : 1.f);
+      b = (b * inv) * (nw ? nw[ib] : 1.f);
     }
     const float cs = cos_sin[(size_t)t * rot + j], sn = cos_sin[(size_t)t * rot + half + j];
-    Elem<T>::store(dst + ia, a * cs - b * sn);
-    Elem<T>::store(dst + ib, b * cs + a * sn);
+    Elem<T>::store(dst + ia, (a * cs - b * sn) * qs);
+    Elem<T>::store(dst + ib, (b * cs + a * sn) * qs);
   }
   for (int c = rot + lane; c < d_pad; c += 32) {
     float x = 0.f;
     if (c < dk) {
-      x = Elem<T>::load(src + c);
-      if (nw) x = (x * inv) * nw[c];
+      x = Elem<T>::load(src + c) + (bias ? bias[c] : 0.f);
+      if (normed) x = (x * inv) * (nw ? nw[c] : 1.f);
+      x *= qs;
     }
     Elem<T>::store(dst + c, x);
   }
@@ -377,8 +417,10 @@ MS_EXPORT int ms_qkv_prepare(void* q_out, void* k_pool, void* v_pool, const void
                              const float* q_norm_w, const float* k_norm_w, const float* cos_sin, const int* positions,
                              const int* row_of_token, const int* page_indptr, const int* page_indices, int num_tokens, int nq,
                              int nkv, int dk, int dv, int d_pad, int rot, int adjacent, float eps, int page_size, int num_pages,
-                             int* status, int dtype, cudaStream_t stream) {
+                             int* status, int dtype, cudaStream_t stream, const float* bias, const float* q_scale, int unit_norm) {
   if (num_tokens == 0) return 0;
+  const PrepareExtras ex{bias, q_scale, unit_norm};
+  MS_CHECK_ARG((k_pool == nullptr) == (v_pool == nullptr), "qkv_prepare: key and value pools come together or not at all");
   MS_CHECK_ARG(nq > 0 && nkv > 0 && dk > 0 && dv > 0 && d_pad >= dk && d_pad >= dv, "qkv_prepare: bad sizes nq=%d nkv=%d dk=%d dv=%d D=%d",
                nq, nkv, dk, dv, d_pad);
   MS_CHECK_ARG(rot >= 0 && rot <= dk && rot % 2 == 0, "qkv_prepare: rot=%d must be even and at most dk=%d", rot, dk);
@@ -386,7 +428,7 @@ MS_EXPORT int ms_qkv_prepare(void* q_out, void* k_pool, void* v_pool, const void
   MS_CHECK_ARG(page_size > 0 && (page_size & (page_size - 1)) == 0, "qkv_prepare: page_size=%d must be a power of two", page_size);
   int page_shift = 0;
   while ((1 << page_shift) < page_size) ++page_shift;
-  const long long items = (long long)num_tokens * (nq + 2 * nkv);
+  const long long items = (long long)num_tokens * (k_pool ? nq + 2 * nkv : nq);
   const int warps = 8;
   const unsigned blocks = (unsigned)((items + warps - 1) / warps);
   if (dtype == MS_BF16 && (adjacent || rot % 16 == 0) && dk % 8 == 0 && dv % 8 == 0 && d_pad % 8 == 0 && ld % 8 == 0 && q_off % 8 == 0 &&
@@ -395,22 +437,22 @@ MS_EXPORT int ms_qkv_prepare(void* q_out, void* k_pool, void* v_pool, const void
     if (adjacent || rot == 0)
       MS_LAUNCH(qkv_prepare_bf16x8_kernel<true>, blocks, warps * 32, 0, stream, (__nv_bfloat16*)q_out, (__nv_bfloat16*)k_pool,
                 (__nv_bfloat16*)v_pool, (const __nv_bfloat16*)proj, ld, q_off, k_off, v_off, q_norm_w, k_norm_w, cos_sin, positions,
-                row_of_token, page_indptr, page_indices, num_tokens, nq, nkv, dk, dv, d_pad, rot, eps, page_shift, num_pages, status);
+                row_of_token, page_indptr, page_indices, num_tokens, nq, nkv, dk, dv, d_pad, rot, eps, page_shift, num_pages, status, ex);
     else  // (the table's rows are rot floats wide: 16-byte loads of eight cosines need rot / 2 a multiple of 8, which rot % 16 gives)
       MS_LAUNCH(qkv_prepare_bf16x8_kernel<false>, blocks, warps * 32, 0, stream, (__nv_bfloat16*)q_out, (__nv_bfloat16*)k_pool,
                 (__nv_bfloat16*)v_pool, (const __nv_bfloat16*)proj, ld, q_off, k_off, v_off, q_norm_w, k_norm_w, cos_sin, positions,
-                row_of_token, page_indptr, page_indices, num_tokens, nq, nkv, dk, dv, d_pad, rot, eps, page_shift, num_pages, status);
+                row_of_token, page_indptr, page_indices, num_tokens, nq, nkv, dk, dv, d_pad, rot, eps, page_shift, num_pages, status, ex);
     return 0;
   }
   if (dtype == MS_F32)
     MS_LAUNCH(qkv_prepare_kernel<float>, blocks, warps * 32, 0, stream, (float*)q_out, (float*)k_pool, (float*)v_pool,
               (const float*)proj, ld, q_off, k_off, v_off, q_norm_w, k_norm_w, cos_sin, positions, row_of_token, page_indptr,
-              page_indices, num_tokens, nq, nkv, dk, dv, d_pad, rot, adjacent, eps, page_shift, num_pages, status);
+              page_indices, num_tokens, nq, nkv, dk, dv, d_pad, rot, adjacent, eps, page_shift, num_pages, status, ex);
   else
     MS_LAUNCH(qkv_prepare_kernel<__nv_bfloat16>, blocks, warps * 32, 0, stream, (__nv_bfloat16*)q_out, (__nv_bfloat16*)k_pool,
               (__nv_bfloat16*)v_pool, (const __nv_bfloat16*)proj, ld, q_off, k_off, v_off, q_norm_w, k_norm_w, cos_sin, positions,
               row_of_token, page_indptr, page_indices, num_tokens, nq, nkv, dk, dv, d_pad, rot, adjacent, eps, page_shift,
-              num_pages, status);
+              num_pages, status, ex);
   return 0;
 }
 

@@ -19,12 +19,15 @@ namespace ms {
 constexpr int ROUTE_THREADS = 128;
 
 // One CTA per token. x [T, K] (rows ld_x apart), router [R, K] float32, correction [R] float32 or null.
-// idx_out [T, top] int32, wgt_out [T, top] float32.
+// idx_out [T, top] int32, wgt_out [T, top] float32. logit_bias [R] float32 or null: added to the logits themselves (it
+// moves scores and weights, where the correction moves the choice alone). gate_w [K] float32 with gate_out [T]: one
+// more product of the same input, gate_out[t] = sigmoid(x . gate_w), the weight of an expert that every token uses.
 template <typename T>
 __global__ void __launch_bounds__(ROUTE_THREADS)
 expert_route_kernel(int* __restrict__ idx_out, float* __restrict__ wgt_out, const T* __restrict__ x, int ld_x,
                     const float* __restrict__ router, const float* __restrict__ correction, int K, int R, int top, int group_count,
-                    int group_keep, float weight_scale, int renormalize) {
+                    int group_keep, float weight_scale, int renormalize, const float* __restrict__ logit_bias,
+                    const float* __restrict__ gate_w, float* __restrict__ gate_out) {
   extern __shared__ float route_smem[];
   float* xs = route_smem;      // [K]
   float* s = xs + K;           // [R] logits, then scores
@@ -40,7 +43,13 @@ expert_route_kernel(int* __restrict__ idx_out, float* __restrict__ wgt_out, cons
     float acc = 0.f;
     for (int k = lane; k < K; k += 32) acc = fmaf(xs[k], w[k], acc);
     acc = warp_sum(acc);
-    if (lane == 0) s[e] = acc;
+    if (lane == 0) s[e] = acc + (logit_bias ? logit_bias[e] : 0.f);
+  }
+  if (gate_w && warp == ROUTE_THREADS / 32 - 1) {
+    float acc = 0.f;
+    for (int k = lane; k < K; k += 32) acc = fmaf(xs[k], gate_w[k], acc);
+    acc = warp_sum(acc);
+    if (lane == 0) gate_out[t] = 1.0f / (1.0f + expf(-acc));
   }
   __syncthreads();
   if (warp != 0) return;
@@ -378,7 +387,8 @@ expert_gemm_mma_kernel(void* __restrict__ out_, const __nv_bfloat16* __restrict_
 template <typename T>
 __global__ void expert_combine_kernel(T* __restrict__ out, const float* __restrict__ y, const T* __restrict__ x, int ld_x,
                                       const int* __restrict__ idx, const float* __restrict__ wgt, const int* __restrict__ pos,
-                                      long long total, int H, int top, int E) {
+                                      long long total, int H, int top, int E, const T* __restrict__ shared,
+                                      const float* __restrict__ shared_gate) {
   pdl_prologue();
   const long long i = (long long)blockIdx.x * blockDim.x + threadIdx.x;
   if (i >= total) return;
@@ -393,6 +403,7 @@ __global__ void expert_combine_kernel(T* __restrict__ out, const float* __restri
     else if (idx[slot] >= E) v = Elem<T>::load(x + t * ld_x + c);
     acc = fmaf(wgt[slot], v, acc);
   }
+  if (shared) acc = fmaf(shared_gate ? shared_gate[t] : 1.f, Elem<T>::load(shared + i), acc);  // the expert every token uses
   Elem<T>::store(out + i, acc);
 }
 
@@ -405,7 +416,7 @@ MS_DEFINE_PDL_SWITCH(ms_experts_set_pdl)
 
 MS_EXPORT int ms_expert_route(int* idx, float* wgt, const void* x, int ld_x, const float* router, const float* correction, int tokens,
                               int K, int R, int top, int group_count, int group_keep, float weight_scale, int renormalize, int dtype,
-                              cudaStream_t stream) {
+                              cudaStream_t stream, const float* logit_bias, const float* gate_w, float* gate_out) {
   if (tokens == 0) return 0;
   MS_CHECK_ARG(R >= 1 && top >= 1 && top <= R && K >= 1, "expert_route: top %d of %d router outputs", top, R);
   MS_CHECK_ARG(group_count >= 1 && R % group_count == 0 && group_keep >= 1 && group_keep <= group_count &&
@@ -416,12 +427,12 @@ MS_EXPORT int ms_expert_route(int* idx, float* wgt, const void* x, int ld_x, con
   if (dtype == MS_F32) {
     if (smem > 48 * 1024) MS_CHECK_CUDA(cudaFuncSetAttribute(expert_route_kernel<float>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
     MS_LAUNCH(expert_route_kernel<float>, tokens, ROUTE_THREADS, smem, stream, idx, wgt, (const float*)x, ld_x, router, correction, K, R, top,
-              group_count, group_keep, weight_scale, renormalize);
+              group_count, group_keep, weight_scale, renormalize, logit_bias, gate_w, gate_out);
   } else {
     if (smem > 48 * 1024)
       MS_CHECK_CUDA(cudaFuncSetAttribute(expert_route_kernel<__nv_bfloat16>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
     MS_LAUNCH(expert_route_kernel<__nv_bfloat16>, tokens, ROUTE_THREADS, smem, stream, idx, wgt, (const __nv_bfloat16*)x, ld_x, router,
-              correction, K, R, top, group_count, group_keep, weight_scale, renormalize);
+              correction, K, R, top, group_count, group_keep, weight_scale, renormalize, logit_bias, gate_w, gate_out);
   }
   return 0;
 }
@@ -508,14 +519,16 @@ MS_EXPORT int ms_expert_gemm(void* out, const void* A, int lda, const int* perm,
 }
 
 MS_EXPORT int ms_expert_combine(void* out, const float* y, const void* x, int ld_x, const int* idx, const float* wgt, const int* pos,
-                                int tokens, int H, int top, int E, int dtype, cudaStream_t stream) {
+                                int tokens, int H, int top, int E, int dtype, cudaStream_t stream, const void* shared,
+                                const float* shared_gate) {
   if (tokens == 0) return 0;
   const long long total = (long long)tokens * H;
   const unsigned blocks = (unsigned)((total + 255) / 256);
   if (dtype == MS_F32)
-    MS_LAUNCH(expert_combine_kernel<float>, blocks, 256, 0, stream, (float*)out, y, (const float*)x, ld_x, idx, wgt, pos, total, H, top, E);
+    MS_LAUNCH(expert_combine_kernel<float>, blocks, 256, 0, stream, (float*)out, y, (const float*)x, ld_x, idx, wgt, pos, total, H, top, E,
+              (const float*)shared, shared_gate);
   else
     MS_LAUNCH(expert_combine_kernel<__nv_bfloat16>, blocks, 256, 0, stream, (__nv_bfloat16*)out, y, (const __nv_bfloat16*)x, ld_x, idx, wgt,
-              pos, total, H, top, E);
+              pos, total, H, top, E, (const __nv_bfloat16*)shared, shared_gate);
   return 0;
 }

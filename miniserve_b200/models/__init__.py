@@ -1,2 +1,2 @@
 """Architectures this package ships. Importing the package registers them."""
-from . import fekulix, mugipel, qwen3, rofozen  # noqa: F401
+from . import fekulix, kovusun, mugipel, qwen3, rofozen  # noqa: F401

@@ -13,10 +13,10 @@ from dataclasses import dataclass
 import torch
 
 from . import blas, experts, native
-from .mixers import (act_mul, add_dyt, add_rmsnorm_scaled, add_row_vector, axpby, channel_gate, conv_silu_unit,  # noqa: F401
-                     conv_state_update, decay_scan, gate_relu_squared, gated_group_norm, gelu_tanh, head_gate, head_norm_gate,
-                     latent_prepare, latent_rope_prepare, qkv_prepare, relu_squared, rope_table_scaled, row_rmsnorm, scale_,
-                     ssm_step_decay, stream_concat)
+from .mixers import (act_mul, add_dyt, add_layernorm, add_rmsnorm_scaled, add_row_vector, axpby, channel_gate, clamped_glu,  # noqa: F401
+                     conv_silu_unit, conv_state_update, decay_scan, gate_relu_squared, gated_group_norm, gelu_tanh, head_gate,
+                     head_norm_gate, latent_prepare, latent_rope_prepare, qkv_prepare, relu_squared, rope_table_scaled, row_rmsnorm,
+                     scale_, shift_state_update, ssm_step_decay, stream_concat, sum_bias, token_shift)
 from .native import NativeError, OutOfBlocks
 
 __all__ = [
@@ -462,10 +462,19 @@ class AttentionExtras:
     sink_values: torch.Tensor | None = None
     softcap: float = 0.0
     chunk: int = 0
+    # a distance bias: r1_h * ln(1 + r2_h * (i - j)) is taken off the scaled score of query i and key j (float32 [heads] each)
+    dist_r1: torch.Tensor | None = None
+    dist_r2: torch.Tensor | None = None
+    keep_first: int = 0  # the first keep_first keys of a sequence stay visible behind the window
 
     @property
     def any(self) -> bool:
-        return self.sink_values is not None or bool(self.softcap) or bool(self.chunk)
+        return self.sink_values is not None or bool(self.softcap) or bool(self.chunk) or self.positional
+
+    @property
+    def positional(self) -> bool:
+        """Whether it has a part that only some kernels take (a distance bias, kept first keys)."""
+        return self.dist_r1 is not None or bool(self.keep_first)
 
 
 NO_EXTRAS = AttentionExtras()
@@ -480,6 +489,9 @@ def attention_rowwise(out: torch.Tensor, q: torch.Tensor, k_pool: torch.Tensor, 
     _check_dev(out, q, k_pool, v_pool, positions, row_of_token, page_indptr, page_indices, status)
     extras = extras or NO_EXTRAS
     assert extras.sink_values is None or (extras.sink_values.dtype == torch.float32 and extras.sink_values.numel() == q.shape[1])
+    for r in (extras.dist_r1, extras.dist_r2):
+        assert r is None or (r.dtype == torch.float32 and r.numel() == q.shape[1] and r.is_cuda and r.is_contiguous())
+    assert (extras.dist_r1 is None) == (extras.dist_r2 is None)
     t, nq, d = q.shape
     nkv, page_size = k_pool.shape[1], k_pool.shape[2]
     assert out.shape == q.shape and k_pool.shape[3] == d and k_pool.dtype == q.dtype
@@ -488,7 +500,7 @@ def attention_rowwise(out: torch.Tensor, q: torch.Tensor, k_pool: torch.Tensor, 
         _ptr(out), _ptr(q), _ptr(k_pool), _ptr(v_pool), _ptr(positions), _ptr(row_of_token), _ptr(page_indptr),
         _ptr(page_indices), t, nq, nkv, d, float(scale), int(window or 0), int(sink or extras.sink_values is not None), page_size,
         k_pool.shape[0], _ptr(status), dtype_code(q.dtype), _stream(stream), _ptr(extras.sink_values), float(extras.softcap or 0.0),
-        int(extras.chunk or 0)))
+        int(extras.chunk or 0), _ptr(extras.dist_r1), _ptr(extras.dist_r2), int(extras.keep_first or 0)))
 
 
 def nucleus_bytes() -> int:
@@ -529,7 +541,7 @@ def attention(out: torch.Tensor, q: torch.Tensor, k_pool: torch.Tensor, v_pool: 
     from . import attention_bf16
 
     extras = extras if extras is not None and extras.any else None
-    if extras is not None and not (q.dtype == torch.bfloat16 and attention_bf16.takes_extras(q.shape[2], k_pool.shape[2])):
+    if extras is not None and (extras.positional or not (q.dtype == torch.bfloat16 and attention_bf16.takes_extras(q.shape[2], k_pool.shape[2]))):
         attention_rowwise(out, q, k_pool, v_pool, ctx.positions, ctx.row_of_token, ctx.page_indptr[group],
                           ctx.page_indices[group], scale, window, ctx.status, stream=ctx.stream, sink=sink, extras=extras)
         return

@@ -23,20 +23,24 @@ def tc_experts_ok(dtype, hidden: int, inter: int, activation: str) -> bool:
 
 
 def expert_route(idx, wgt, x, router, correction, top: int, group_count: int, group_keep: int, weight_scale: float,
-                 renormalize: bool, stream=None) -> None:
+                 renormalize: bool, stream=None, logit_bias=None, gate_w=None, gate_out=None) -> None:
     """idx [T, top] int32 and wgt [T, top] float32: each token's chosen router outputs and their weights.
     Logits ``x router^T`` in float32 (``router`` [R, K] float32), scores their softmax, choice scores the scores plus
     ``correction`` [R] (float32, or None); the R outputs form ``group_count`` equal groups of neighbours of which the
     ``group_keep`` with the largest choice score in them can be chosen from; weights are the chosen scores (without
-    the correction) times ``weight_scale``, divided by their sum if ``renormalize``. Ties go to the lower index."""
+    the correction) times ``weight_scale``, divided by their sum if ``renormalize`` (which makes them the softmax over
+    the chosen logits alone). Ties go to the lower index. ``logit_bias`` [R] float32 is added to the logits themselves.
+    ``gate_w`` [K] float32 with ``gate_out`` [T] float32: gate_out[t] = sigmoid(x[t] . gate_w), from the same staged input."""
     t, k = x.shape
     r = router.shape[0]
-    _f32(router, correction, wgt)
+    _f32(router, correction, wgt, logit_bias, gate_w, gate_out)
+    assert (gate_w is None) == (gate_out is None) and (gate_w is None or (gate_w.numel() == k and gate_out.numel() >= t))
+    assert logit_bias is None or logit_bias.numel() == r
     assert router.shape == (r, k) and idx.shape == (t, top) and wgt.shape == (t, top) and idx.dtype == torch.int32
     assert idx.is_contiguous() and (correction is None or correction.numel() == r)
     native.experts_check(native.experts().ms_expert_route(
         _ptr(idx), _ptr(wgt), _ptr(x), _rows(x), _ptr(router), _ptr(correction), t, k, r, top, group_count, group_keep,
-        float(weight_scale), int(renormalize), _dt(x.dtype), _stream(stream)))
+        float(weight_scale), int(renormalize), _dt(x.dtype), _stream(stream), _ptr(logit_bias), _ptr(gate_w), _ptr(gate_out)))
 
 
 def expert_max_tiles(slots: int, experts: int, tile_rows: int = TILE_ROWS) -> int:
@@ -106,13 +110,16 @@ def expert_down(out, act, w_down, tiles, meta, offsets, stream=None) -> None:
         expert_max_tiles(slots, e), hidden, inter, 0, 0, _dt(act.dtype), _stream(stream)))
 
 
-def expert_combine(out, y, x, idx, wgt, pos, experts: int, stream=None) -> None:
+def expert_combine(out, y, x, idx, wgt, pos, experts: int, stream=None, shared=None, shared_gate=None) -> None:
     """out[t] = sum over the token's choices, in their order, of wgt * (y[pos] for an expert with tensors, x[t] for a
-    router output from ``experts`` on: an identity expert); float32 sum, one rounding."""
+    router output from ``experts`` on: an identity expert); float32 sum, one rounding. ``shared`` [T, H] (the run's
+    dtype): the output of an expert that every token uses, added times ``shared_gate`` [T] float32 (or once)."""
     t, hidden = out.shape
     top = idx.shape[1]
     _f32(y, wgt)
     assert out.is_contiguous() and x.shape == (t, hidden) and x.dtype == out.dtype and y.shape[1] == hidden
+    assert shared is None or (shared.shape == (t, hidden) and shared.dtype == out.dtype and shared.is_contiguous())
+    _f32(shared_gate)
     native.experts_check(native.experts().ms_expert_combine(
         _ptr(out), _ptr(y), _ptr(x), _rows(x), _ptr(idx), _ptr(wgt), _ptr(pos), t, hidden, top, experts, _dt(out.dtype),
-        _stream(stream)))
+        _stream(stream), _ptr(shared), _ptr(shared_gate)))

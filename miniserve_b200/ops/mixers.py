@@ -78,29 +78,103 @@ def head_gate(out: torch.Tensor, attn: torch.Tensor, gate: torch.Tensor | None, 
 
 
 def qkv_prepare(q_out, k_pool, v_pool, q, k, v, q_norm_w, k_norm_w, cos_sin, rotary_dim: int, adjacent: bool, eps: float,
-                positions, row_of_token, page_indptr, page_indices, page_size: int, status, stream=None) -> None:
+                positions, row_of_token, page_indptr, page_indices, page_size: int, status, stream=None, bias=None,
+                unit_norm: bool = False, q_scale=None) -> None:
     """Per-head RMS norm of q and k (float32 weights or None), rotation of the first ``rotary_dim`` channels
     (pairs (2i, 2i+1) if ``adjacent`` else (i, i + rotary_dim/2)) by the step's cos/sin table, q to
     ``q_out`` [T, nq, D] and k, v into their pages [pages, nkv, page_size, D], zero beyond their own
-    sizes. ``q`` [T, nq*dk], ``k`` [T, nkv*dk], ``v`` [T, nkv*dv]: views into one projection's rows."""
+    sizes. ``q`` [T, nq*dk], ``k`` [T, nkv*dk], ``v`` [T, nkv*dv]: views into one projection's rows.
+    ``bias``: float32 [nq*dk + nkv*dk + nkv*dv], the projections' biases in the order q, k, v, added first.
+    ``unit_norm``: q and k are divided by their root mean square also without norm weights. ``q_scale``: float32 [nq],
+    a factor per query head applied last. Without pools (``k_pool``, ``k`` and ``v`` None) only the queries are
+    prepared (a mixer that reads another's keys and values); ``bias`` is then [nq*dk]."""
     t, nq, d = q_out.shape
+    dk = q.shape[1] // nq
+    _f32(q_norm_w, k_norm_w, cos_sin, bias, q_scale)
+    assert cos_sin is None or cos_sin.shape == (t, rotary_dim)
+    assert q_scale is None or q_scale.numel() == nq
+    if k_pool is None:
+        assert k is None and v is None and v_pool is None and q.shape == (t, nq * dk) and q.dtype == q_out.dtype
+        assert bias is None or bias.numel() == nq * dk
+        native.mixers_check(native.mixers().ms_qkv_prepare(
+            _ptr(q_out), None, None, q.data_ptr(), _rows(q), 0, 0, 0, _ptr(q_norm_w), None, _ptr(cos_sin), _ptr(positions),
+            _ptr(row_of_token), _ptr(page_indptr), _ptr(page_indices), t, nq, 1, dk, dk, d, rotary_dim if cos_sin is not None else 0,
+            int(adjacent), float(eps), page_size, 0, _ptr(status), _dt(q.dtype), _stream(stream), _ptr(bias), _ptr(q_scale),
+            int(unit_norm)))
+        return
     nkv = k_pool.shape[1]
-    dk, dv = q.shape[1] // nq, v.shape[1] // nkv
+    dv = v.shape[1] // nkv
     assert k.shape == (t, nkv * dk) and q.shape == (t, nq * dk) and v.shape == (t, nkv * dv)
     assert k_pool.shape == v_pool.shape and k_pool.shape[2] == page_size and k_pool.shape[3] == d
     assert q.dtype == k.dtype == v.dtype == q_out.dtype == k_pool.dtype
+    assert bias is None or bias.numel() == (nq + nkv) * dk + nkv * dv
     ld = _rows(q)
     assert _rows(k) == ld and _rows(v) == ld, "q, k and v must be columns of the same rows"
     item = q.element_size()
     base = min(q.data_ptr(), k.data_ptr(), v.data_ptr())
     offs = [(x.data_ptr() - base) // item for x in (q, k, v)]
-    _f32(q_norm_w, k_norm_w, cos_sin)
-    assert cos_sin is None or cos_sin.shape == (t, rotary_dim)
     native.mixers_check(native.mixers().ms_qkv_prepare(
         _ptr(q_out), _ptr(k_pool), _ptr(v_pool), base, ld, offs[0], offs[1], offs[2], _ptr(q_norm_w), _ptr(k_norm_w),
         _ptr(cos_sin), _ptr(positions), _ptr(row_of_token), _ptr(page_indptr), _ptr(page_indices), t, nq, nkv, dk, dv, d,
         rotary_dim if cos_sin is not None else 0, int(adjacent), float(eps), page_size, k_pool.shape[0], _ptr(status),
-        _dt(q.dtype), _stream(stream)))
+        _dt(q.dtype), _stream(stream), _ptr(bias), _ptr(q_scale), int(unit_norm)))
+
+
+def add_layernorm(out, residual, delta, weight, bias, eps: float, rows=None, num_rows=None, write_residual=True, delta_scale: float = 1.0,
+                  out2=None, weight2=None, bias2=None, stream=None) -> None:
+    """out[i] = (h - mean(h)) / sqrt(mean((h - mean(h))^2) + eps) * weight + bias with h = residual[r] + delta_scale *
+    delta[r], r = rows[i] (or i); h is written back to ``residual`` when there is no gather. ``out2`` with ``weight2``
+    and ``bias2``: a second norm of the same rows (the statistics are computed once). float32 arithmetic and parameters."""
+    _f32(residual, weight, bias, weight2, bias2)
+    hidden = residual.shape[-1]
+    n = out.shape[0] if num_rows is None else num_rows
+    assert out.is_contiguous() and out.shape[-1] == hidden and weight.numel() == hidden and bias.numel() == hidden
+    assert delta is None or (delta.dtype == out.dtype and delta.is_contiguous())
+    assert out2 is None or (out2.shape == out.shape and out2.dtype == out.dtype and out2.is_contiguous() and weight2.numel() == hidden
+                            and bias2.numel() == hidden)
+    native.mixers_check(native.mixers().ms_add_layernorm(
+        _ptr(out), _ptr(out2), _ptr(residual), _ptr(delta), float(delta_scale), _ptr(weight), _ptr(bias), _ptr(weight2), _ptr(bias2),
+        _ptr(rows), float(eps), n, hidden, int(write_residual and rows is None), _dt(out.dtype), _stream(stream)))
+
+
+def token_shift(out, h, state, mix, ctx) -> None:
+    """out[t] = h[t] + (h[t - 1] - h[t]) * mix (float32 [width]); the token before a row's first one in this step is the
+    row's slot of ``state`` [slots, width], or zeros where the row starts its sequence. ``out`` is not ``h``."""
+    t, width = h.shape
+    _f32(mix)
+    assert out.shape == h.shape and out.dtype == h.dtype == state.dtype and out.is_contiguous() and h.is_contiguous()
+    assert state.is_contiguous() and state.shape[1] == width and mix.numel() == width and out.data_ptr() != h.data_ptr()
+    native.mixers_check(native.mixers().ms_token_shift(
+        _ptr(out), _ptr(h), _ptr(state), _ptr(mix), _ptr(ctx.row_of_token), _ptr(ctx.cu_q), _ptr(ctx.q_start), _ptr(ctx.state_slot),
+        t, width, _dt(h.dtype), ctx.stream))
+
+
+def shift_state_update(state, h, ctx) -> None:
+    """state[slot of row] = h[the row's last token of this step], for every row of the step."""
+    assert h.is_contiguous() and state.is_contiguous() and state.dtype == h.dtype and state.shape[1] == h.shape[1]
+    native.mixers_check(native.mixers().ms_shift_state_update(
+        _ptr(state), _ptr(h), _ptr(ctx.cu_q), _ptr(ctx.state_slot), ctx.num_rows, h.shape[1], _dt(h.dtype), ctx.stream))
+
+
+def clamped_glu(out, gate_up, bias, limit: float, alpha: float, shift: float, stream=None) -> None:
+    """out[t, c] = g * sigmoid(alpha * g) * (u + shift), g = min(gate_up[t, c] + bias[c], limit), u = clamp(gate_up[t, I + c] +
+    bias[I + c], -limit, limit); ``bias`` float32 [2 I] or None; ``limit`` 0: no clamps. float32 arithmetic, one rounding."""
+    t, inter = out.shape
+    _f32(bias)
+    assert gate_up.shape == (t, 2 * inter) and gate_up.dtype == out.dtype and out.is_contiguous() and gate_up.is_contiguous()
+    assert bias is None or bias.numel() == 2 * inter
+    native.mixers_check(native.mixers().ms_clamped_glu(_ptr(out), _ptr(gate_up), _ptr(bias), t, inter, float(limit), float(alpha),
+                                                       float(shift), _dt(out.dtype), _stream(stream)))
+
+
+def sum_bias(out, a, b=None, vec=None, stream=None) -> None:
+    """out = a (+ b) (+ vec on every row); a, b and out [rows, width] in the run's dtype (out may be a), vec float32 [width]."""
+    rows, width = a.shape
+    _f32(vec)
+    assert out.shape == a.shape and out.dtype == a.dtype and out.is_contiguous() and a.is_contiguous()
+    assert b is None or (b.shape == a.shape and b.dtype == a.dtype and b.is_contiguous())
+    assert vec is None or vec.numel() == width
+    native.mixers_check(native.mixers().ms_sum_bias(_ptr(out), _ptr(a), _ptr(b), _ptr(vec), rows, width, _dt(a.dtype), _stream(stream)))
 
 
 def decay_scan(o_out, state, q, k, v, z, z_bias, decay_coef, z_sign: float, beta, ctx, heads: int, dk: int, dv: int,

@@ -110,7 +110,7 @@ def kernels():
     _declare(lib, "ms_gemm_f32", [_p, _p, _p, _i, _i, _i, _i, _i, _i, _p])
     _declare(lib, "ms_gemm_f32_batched", [_p, _p, _p, _i, _i, _i, _i, _i, _i, _i, _ll, _ll, _ll, _p])
     _declare(lib, "ms_attention_rowwise",
-             [_p, _p, _p, _p, _p, _p, _p, _p, _i, _i, _i, _i, _f, _i, _i, _i, _i, _p, _i, _p, _p, _f, _i])
+             [_p, _p, _p, _p, _p, _p, _p, _p, _i, _i, _i, _i, _f, _i, _i, _i, _i, _p, _i, _p, _p, _f, _i, _p, _p, _i])
     _declare(lib, "ms_nucleus_bytes", [])
     _declare(lib, "ms_sample_scratch_bytes", [_i, _i], _ll)
     _declare(lib, "ms_sample", [_p, _p, _p, _p, _p, _p, _p, _p, _i, _i, _p])
@@ -128,7 +128,7 @@ def mixers():
     _declare(lib, "ms_scale_f32", [_p, _f, _ll, _p])
     _declare(lib, "ms_axpby", [_p, _p, _p, _f, _f, _ll, _i, _p])
     _declare(lib, "ms_head_gate", [_p, _i, _p, _p, _i, _i, _i, _i, _i, _f, _i, _p])
-    _declare(lib, "ms_qkv_prepare", [_p] * 4 + [_i] * 4 + [_p] * 7 + [_i] * 8 + [_f, _i, _i, _p, _i, _p])
+    _declare(lib, "ms_qkv_prepare", [_p] * 4 + [_i] * 4 + [_p] * 7 + [_i] * 8 + [_f, _i, _i, _p, _i, _p, _p, _p, _i])
     _declare(lib, "ms_add_rmsnorm_scaled", [_p, _p, _p, _f, _p, _f, _p, _f, _i, _i, _i, _i, _p])
     _declare(lib, "ms_stream_concat", [_p, _p, _p, _f, _p, _p, _i, _i, _i, _i, _i, _i, _p])
     _declare(lib, "ms_add_row_vector", [_p, _p, _i, _i, _p])
@@ -140,6 +140,11 @@ def mixers():
     _declare(lib, "ms_row_rmsnorm", [_p, _i, _p, _i, _p, _i, _i, _f, _i, _p])
     _declare(lib, "ms_latent_rope_prepare", [_p, _p, _i, _p, _f, _p, _i, _i, _i, _p, _p, _p, _p, _p, _p, _i, _i, _i, _i, _i, _i, _p, _i, _p])
     _declare(lib, "ms_act_mul", [_p, _p, _i, _i, _i, _i, _p])
+    _declare(lib, "ms_add_layernorm", [_p, _p, _p, _p, _f, _p, _p, _p, _p, _p, _f, _i, _i, _i, _i, _p])
+    _declare(lib, "ms_token_shift", [_p, _p, _p, _p, _p, _p, _p, _p, _i, _i, _i, _p])
+    _declare(lib, "ms_shift_state_update", [_p, _p, _p, _p, _i, _i, _i, _p])
+    _declare(lib, "ms_clamped_glu", [_p, _p, _p, _i, _i, _f, _f, _f, _i, _p])
+    _declare(lib, "ms_sum_bias", [_p, _p, _p, _p, _i, _i, _i, _p])
     return lib
 
 
@@ -168,14 +173,14 @@ def experts():
     _declare(lib, "ms_experts_last_error", [], c_char_p)
     _declare(lib, "ms_experts_set_pdl", [_i], None)
     lib.ms_experts_set_pdl(int(pdl_enabled()))
-    _declare(lib, "ms_expert_route", [_p, _p, _p, _i, _p, _p, _i, _i, _i, _i, _i, _i, _f, _i, _i, _p])
+    _declare(lib, "ms_expert_route", [_p, _p, _p, _i, _p, _p, _i, _i, _i, _i, _i, _i, _f, _i, _i, _p, _p, _p, _p])
     _declare(lib, "ms_expert_max_tiles", [_i, _i])
     _declare(lib, "ms_expert_plan", [_p, _p, _p, _p, _p, _p, _i, _i, _p])
     _declare(lib, "ms_expert_max_tiles_of", [_i, _i, _i])
     _declare(lib, "ms_expert_plan_of", [_p, _p, _p, _p, _p, _p, _i, _i, _i, _p])
     _declare(lib, "ms_expert_gather", [_p, _p, _i, _p, _p, _i, _i, _i, _p])
     _declare(lib, "ms_expert_gemm", [_p, _p, _i, _p, _i, _p, _p, _p, _p, _i, _i, _i, _i, _i, _i, _p])
-    _declare(lib, "ms_expert_combine", [_p, _p, _p, _i, _p, _p, _p, _i, _i, _i, _i, _i, _p])
+    _declare(lib, "ms_expert_combine", [_p, _p, _p, _i, _p, _p, _p, _i, _i, _i, _i, _i, _p, _p, _p])
     return lib
 
 

@@ -37,11 +37,21 @@ class GQAttention(Part):
     the scale), ``chunk`` (a query at position p sees only keys from floor(p / chunk) * chunk on, blocks counted
     from position 0 of the sequence; the cache then gives back pages that lie a whole block behind), and
     ``out_gate`` = ``channel_sigmoid`` (attention's output is multiplied element by element by sigmoid(W_g x),
-    W_g as wide as the concatenated heads). All of them take the general path."""
+    W_g as wide as the concatenated heads). All of them take the general path.
+
+    And: ``qk_norm`` = ``"unit"`` (q and k are divided by their root mean square over the head, no weight), ``qkv_bias``
+    (q, k and v have biases, tensors ``q_bias`` / ``k_bias`` / ``v_bias`` of ``names``, added in float32 before the norm),
+    ``head_temperature`` (a learned number per head, tensor ``temp``, multiplies the scaled scores: applied to the
+    prepared queries), ``distance_bias`` (tensors ``r1`` and ``r2`` [heads]: r1_h ln(1 + r2_h (i - j)) is taken off the
+    scaled score of query i and key j), ``keep_first`` (the first keys of a sequence stay visible behind the window;
+    the cache then keeps every page) and ``cache_window`` (how far back the cache keeps keys when that is not the
+    mixer's own reach: 0 for everything, for a mixer whose cache another mixer with a longer reach reads). With
+    ``kv_source`` = ``shared`` these run on the general path too: the projection holds q (and the gate) alone."""
     shape_static = True
     input_weight = "w_qkv"  # the attribute that holds the input product's (stacked) matrix; its first ``input_rows`` rows are real
     NAMES = dict(q="q_proj.weight", k="k_proj.weight", v="v_proj.weight", o="o_proj.weight", q_norm="q_norm.weight",
-                 k_norm="k_norm.weight", gate="g_proj.weight", sink="sink")
+                 k_norm="k_norm.weight", gate="g_proj.weight", sink="sink", q_bias="q_proj.bias", k_bias="k_proj.bias",
+                 v_bias="v_proj.bias", temp="temperature", r1="distance.r1", r2="distance.r2")
 
     def __init__(self, spec, env):
         super().__init__(spec, env)
@@ -49,7 +59,8 @@ class GQAttention(Part):
         self.heads = param(spec, "heads", int)
         self.kv_heads = param(spec, "kv_heads", int)
         self.head_dim = param(spec, "head_dim", int)
-        self.qk_norm = bool(spec.get("qk_norm", False))
+        self.unit_norm = spec.get("qk_norm") == "unit"  # a norm without weights
+        self.qk_norm = bool(spec.get("qk_norm", False)) and not self.unit_norm
         self.qk_norm_eps = float(spec.get("qk_norm_eps", 0.0))
         self.window = spec.get("window")
         self.scale = float(spec.get("scale") or self.head_dim ** -0.5)
@@ -72,14 +83,21 @@ class GQAttention(Part):
         self.out_gate = spec.get("out_gate")
         if self.out_gate not in (None, "head_sigmoid", "channel_sigmoid"):
             raise ValueError(f"out_gate must be 'head_sigmoid', 'channel_sigmoid' or absent, got {self.out_gate!r}")
+        self.qkv_bias = bool(spec.get("qkv_bias", False))
+        self.head_temperature = bool(spec.get("head_temperature", False))
+        self.distance_bias = bool(spec.get("distance_bias", False))
+        self.keep_first = int(spec.get("keep_first") or 0)
+        self.cache_window = spec.get("cache_window")
+        if self.keep_first < 0 or (self.keep_first and not self.window):
+            raise ValueError(f"keep_first={self.keep_first} needs a window that it reaches behind")
         self.names = {**self.NAMES, **dict(spec.get("names") or {})}
         self.adjacent = getattr(self.position, "pairing", "halves") == "adjacent"  # how the position encoding pairs channels
         self.general = bool(self.out_gate or self.value_dim != self.head_dim or self.adjacent or self.learned_sink or self.softcap
-                            or self.chunk or getattr(self.position, "table_only", False))
+                            or self.chunk or getattr(self.position, "table_only", False) or self.unit_norm or self.qkv_bias
+                            or self.head_temperature or self.distance_bias or self.keep_first or spec.get("general"))
         self.w_sink = None
         self.extras = None
-        if self.general and not self.owns_cache:
-            raise ValueError("a gate, a value size of its own or adjacent rotation pairs need a cache of the mixer's own")
+        self.w_bias = self.w_temp = None
         # the general path keeps keys and values in one head size: the larger of the two, in steps of 16
         self.cache_dim = -(-max(self.head_dim, self.value_dim) // 16) * 16 if self.general else self.head_dim
         self.feature_width = self.heads * self.value_dim
@@ -96,8 +114,16 @@ class GQAttention(Part):
         if not self.owns_cache:
             return None
         # keys a whole block behind the newest token are never seen again: the cache treats the block as a window
-        reach = min(int(self.window), self.chunk) if self.window and self.chunk else (int(self.window) if self.window else self.chunk)
+        reach = self._own_reach()
+        if self.keep_first:
+            reach = 0  # the kept first keys are read for as long as the request runs: no page is given back
+        if self.cache_window is not None:
+            reach = int(self.cache_window)
         return PagedKV(self.kv_heads, self.cache_dim, reach or None)
+
+    def _own_reach(self) -> int:
+        """How many keys back this mixer's own mask reaches (0: all of them)."""
+        return min(int(self.window), self.chunk) if self.window and self.chunk else (int(self.window) if self.window else self.chunk)
 
     def weights(self):
         d, n = self.head_dim, self.names
@@ -110,6 +136,16 @@ class GQAttention(Part):
             w[n["gate"]] = WeightDecl((self.gate_width, self.hidden))
         if self.learned_sink:
             w[n["sink"]] = WeightDecl((self.heads,), precision="float32")
+        if self.qkv_bias:
+            w[n["q_bias"]] = WeightDecl((self.heads * d,), precision="float32")
+            if self.owns_cache:
+                w[n["k_bias"]] = WeightDecl((self.kv_heads * d,), precision="float32")
+                w[n["v_bias"]] = WeightDecl((self.kv_heads * self.value_dim,), precision="float32")
+        if self.head_temperature:
+            w[n["temp"]] = WeightDecl((self.heads,), precision="float32", init="ones_normal")
+        if self.distance_bias:
+            w[n["r1"]] = WeightDecl((self.heads,), precision="float32")
+            w[n["r2"]] = WeightDecl((self.heads,), precision="float32", init="ones_normal")
         if self.qk_norm:
             # the general kernel takes the norm's weights in float32, the others in the run's dtype
             kind = dict(precision="float32") if self.general else {}
@@ -120,36 +156,42 @@ class GQAttention(Part):
 
     def _stack(self) -> tuple[str, tuple[str, ...]]:
         n = self.names
-        return "qkv_proj.weight", (n["q"], n["k"], n["v"]) + ((n["gate"],) if self.out_gate else ())
+        kv = (n["k"], n["v"]) if self.owns_cache else ()
+        return "qkv_proj.weight", (n["q"],) + kv + ((n["gate"],) if self.out_gate else ())
 
     def stacks(self):
         # one product makes q, k and v (miniserve/model/fused.py:41-95 joins the same rows), and the gate
-        return dict([self._stack()]) if self.owns_cache else {}
+        return dict([self._stack()]) if self.owns_cache or self.out_gate else {}
 
     def bind(self, tensors):
         n = self.names
-        if self.owns_cache:
+        if self.owns_cache or self.out_gate:
             self.w_qkv = self.joined(tensors, *self._stack())
-            self.input_rows = self.w_qkv.shape[0]  # rows of the input product that are this mixer's (before any padding)
-            if self.general and self.w_qkv.shape[0] % 8:
-                # rows of the product's output start on 16 bytes: a few zero rows at the end
-                pad = torch.zeros((-self.w_qkv.shape[0] % 8, self.hidden), dtype=self.w_qkv.dtype, device=self.w_qkv.device)
-                self.w_qkv = torch.cat((self.w_qkv, pad), dim=0).contiguous()
         else:
             self.w_qkv = tensors[n["q"]].contiguous()
+        self.input_rows = self.w_qkv.shape[0]  # rows of the input product that are this mixer's (before any padding)
+        if self.general and self.w_qkv.shape[0] % 8:
+            # rows of the product's output start on 16 bytes: a few zero rows at the end
+            pad = torch.zeros((-self.w_qkv.shape[0] % 8, self.hidden), dtype=self.w_qkv.dtype, device=self.w_qkv.device)
+            self.w_qkv = torch.cat((self.w_qkv, pad), dim=0).contiguous()
         self.w_o = tensors[n["o"]].contiguous()
         self.w_q_norm = tensors[n["q_norm"]].contiguous() if self.qk_norm else None
         self.w_k_norm = tensors[n["k_norm"]].contiguous() if self.qk_norm and self.owns_cache else None
         self.w_sink = tensors[n["sink"]].float().contiguous() if self.learned_sink else None
-        if self.learned_sink or self.softcap or self.chunk:
-            self.extras = ops.AttentionExtras(self.w_sink, self.softcap, self.chunk)
+        if self.qkv_bias:
+            parts = (n["q_bias"], n["k_bias"], n["v_bias"]) if self.owns_cache else (n["q_bias"],)
+            self.w_bias = torch.cat([tensors[p].float().reshape(-1) for p in parts]).contiguous()
+        self.w_temp = tensors[n["temp"]].float().contiguous() if self.head_temperature else None
+        r1 = tensors[n["r1"]].float().contiguous() if self.distance_bias else None
+        r2 = tensors[n["r2"]].float().contiguous() if self.distance_bias else None
+        if self.learned_sink or self.softcap or self.chunk or self.distance_bias or self.keep_first:
+            self.extras = ops.AttentionExtras(self.w_sink, self.softcap, self.chunk, r1, r2, self.keep_first)
 
     @property
     def reach(self) -> int | None:
         """How far back the cache keeps keys for this mixer (what the kernels take as their window): the window, or the
         block of a mask by blocks (which then does the masking itself, inside that reach)."""
-        need = self.cache_need()
-        return need.window if need is not None else (int(self.window) if self.window else None)
+        return self._own_reach() or None
 
     def features(self, x: torch.Tensor, ctx, cache, out: torch.Tensor | None, scale: float = 1.0, proj: torch.Tensor | None = None,
                  defer_gate: bool = False):
@@ -163,13 +205,16 @@ class GQAttention(Part):
         nq, nkv, dk, dv, dc = self.heads, self.kv_heads, self.head_dim, self.value_dim, self.cache_dim
         if proj is None:
             proj = ops.linear(x, self.w_qkv, stream=ctx.stream, out=ctx.buffer("attn.qkv", (t, self.w_qkv.shape[0]), dt, dev))
-        at_k, at_v, at_g = nq * dk, (nq + nkv) * dk, (nq + nkv) * dk + nkv * dv
+        at_k = nq * dk
+        at_v, at_g = ((nq + nkv) * dk, (nq + nkv) * dk + nkv * dv) if self.owns_cache else (at_k, at_k)
         q = ctx.buffer("attn.q", (t, nq, dc), dt, dev)
         _, rotary_dim = self.position.kernel_table()
-        ops.qkv_prepare(q, cache.k, cache.v, proj[:, :at_k], proj[:, at_k:at_v], proj[:, at_v:at_g], self.w_q_norm, self.w_k_norm,
+        own = self.owns_cache  # else the keys and values are another entry's, as its cache holds them
+        ops.qkv_prepare(q, cache.k if own else None, cache.v if own else None, proj[:, :at_k], proj[:, at_k:at_v] if own else None,
+                        proj[:, at_v:at_g] if own else None, self.w_q_norm, self.w_k_norm,
                         self.position.step_table(ctx), rotary_dim, self.adjacent, self.qk_norm_eps,
                         ctx.positions, ctx.row_of_token, ctx.page_indptr[cache.group], ctx.page_indices[cache.group],
-                        cache.page_size, ctx.status, stream=ctx.stream)
+                        cache.page_size, ctx.status, stream=ctx.stream, bias=self.w_bias, unit_norm=self.unit_norm, q_scale=self.w_temp)
         att = ctx.buffer("attn.out", (t, nq, dc), dt, dev)
         ops.attention(att, q, cache.k, cache.v, ctx, cache.group, self.scale, self.reach, self.sink, extras=self.extras)
         if self.out_gate == "channel_sigmoid":

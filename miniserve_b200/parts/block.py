@@ -5,8 +5,8 @@ from __future__ import annotations
 import torch
 
 from .. import ops
-from ..config.spec import LayerSpec
-from .base import BuildEnv, Part, ResidualStream, build_part, register_part
+from ..config.spec import LayerSpec, PartSpec
+from .base import BuildEnv, FixedState, Part, ResidualStream, WeightDecl, build_part, register_part
 
 
 def _norm(norm, stream: ResidualStream, ctx):
@@ -140,6 +140,93 @@ class ParallelResidualBlock(Part):
         y = ctx.buffer("block.out", tuple(a.shape), dt, dev)
         ops.axpby(y, a, b, 1.0, 1.0, stream=ctx.stream)
         return ResidualStream(total, y, self.mult)
+
+
+class TokenShift(Part):
+    """h_t <- h_t + (h_(t-1) - h_t) * mix, element by element, with h_(t-1) the previous token's h before the
+    replacement and zeros before a sequence's first token. The last h of a portion is a request's state (one vector per
+    run entry, in the run's dtype), so that the next portion or the next decoded token continues from it. ``mix`` is a
+    float32 tensor [size]. Parameters: ``size``, ``name`` (the tensor's name)."""
+    shape_static = True
+
+    def __init__(self, spec, env):
+        super().__init__(spec, env)
+        self.size = int(spec["size"])
+        self.name = spec.get("name", "shift")
+
+    def weights(self):
+        return {self.name: WeightDecl((self.size,), precision="float32")}
+
+    def bind(self, tensors):
+        self.w_mix = tensors[self.name].float().contiguous()
+
+    def cache_need(self) -> FixedState:
+        return FixedState((self.size,), self.env.dtype)
+
+    def forward(self, h: torch.Tensor, ctx, cache) -> torch.Tensor:
+        out = ctx.buffer("shift.out", tuple(h.shape), h.dtype, h.device)
+        ops.token_shift(out, h, cache.state, self.w_mix, ctx)
+        ops.shift_state_update(cache.state, h, ctx)  # after the read: the first token of a portion and its last may be far apart
+        return out
+
+
+@register_part("block", "parallel_dual_norm")
+class ParallelDualNormBlock(Part):
+    """x += mixer(shift(norm1(x))) + feed_forward(norm2(x)): both sublayers read the same x, each through a norm of its
+    own; the sum is handed on as the pending addend, so the add happens in float32 inside the next norm. When both
+    norms are layer norms they come out of one launch. ``token_shift`` (a name, or absent): what the mixer reads is
+    first mixed with the previous token's (``TokenShift``); the block then needs a state vector per request beside the
+    mixer's cache, and its cache view is the pair (shift state, mixer's view). A layer without a feed-forward has
+    neither it nor norm2. Parameters: ``names`` (mixer / feed_forward / norm1 / norm2 -> tensor-name prefixes),
+    ``token_shift``, ``hidden``."""
+    shape_static = True
+
+    def __init__(self, spec, env: BuildEnv, layer: LayerSpec | None = None):
+        super().__init__(spec, env)
+        if layer is None:
+            raise ValueError("a block is built from its LayerSpec (use build_block)")
+        names = dict(spec.get("names") or {})
+        self.has_ff = layer.feed_forward is not None
+        self.names = {k: names[k] for k in ("mixer", "norm1") + (("feed_forward", "norm2") if self.has_ff else ())}
+        self.mixer = build_part("mixer", layer.mixer, env)
+        self.norm1 = build_part("norm", layer.norms["norm1"], env)
+        self.feed_forward = build_part("feed_forward", layer.feed_forward, env) if self.has_ff else None
+        self.norm2 = build_part("norm", layer.norms["norm2"], env) if self.has_ff else None
+        shift = spec.get("token_shift")
+        self.shift = TokenShift(PartSpec("token_shift", dict(size=int(spec["hidden"]), name=shift)), env) if shift else None
+        self.paired = self.has_ff and hasattr(self.norm1, "forward_pair") and type(self.norm1) is type(self.norm2)
+
+    def sub_parts(self):
+        out = {self.names["mixer"]: self.mixer, self.names["norm1"]: self.norm1}
+        if self.has_ff:
+            out.update({self.names["feed_forward"]: self.feed_forward, self.names["norm2"]: self.norm2})
+        if self.shift is not None:
+            out[""] = self.shift
+        return out
+
+    def cache_need(self):
+        """The mixer's need, or with a token shift the pair (the shift's state, the mixer's need: None where the mixer
+        reads another entry's cache)."""
+        need = self.mixer.cache_need()
+        return need if self.shift is None else (self.shift.cache_need(), need)
+
+    def forward(self, stream: ResidualStream, ctx, cache) -> ResidualStream:
+        total = stream.total
+        if self.paired:
+            h1, h2 = self.norm1.forward_pair(self.norm2, total, stream.pending, ctx, delta_scale=stream.pending_scale)
+        else:
+            h1 = _norm(self.norm1, stream, ctx)
+            h2 = self.norm2.forward(total, None, ctx, role="norm.out2") if self.has_ff else None
+        if self.shift is not None:
+            shift_cache, cache = cache
+            h1 = self.shift.forward(h1, ctx, shift_cache)
+        a = self.mixer.forward(h1, ctx, cache)
+        if not self.has_ff:
+            return ResidualStream(total, a)
+        b = self.feed_forward.forward(h2, ctx)
+        y = ctx.buffer("block.out", tuple(a.shape), self.env.dtype, a.device)
+        ops.axpby(y, a, b, 1.0, 1.0, stream=ctx.stream)
+        return ResidualStream(total, y)
 
 
 def build_block(layer: LayerSpec, env: BuildEnv) -> Part:

@@ -9,7 +9,7 @@ from typing import Mapping
 import torch
 
 from ..config.spec import ModelSpec
-from .base import BuildEnv, CacheNeed, ResidualStream, WeightDecl, build_part
+from .base import BuildEnv, CacheNeed, ResidualStream, WeightDecl, build_part, flat_needs
 from .block import build_block
 
 
@@ -20,6 +20,9 @@ class EntryCache:
 
     owner: int
     need: "CacheNeed | tuple | None"  # one need, or a tuple of needs (a mixer made of several)
+    # An entry that owns part of what it uses (a state of its own) and reads the rest from another entry: ``need`` is
+    # a tuple with None where it has nothing of its own, and the view it gets has the views of entry ``shares`` there.
+    shares: int | None = None
 
 
 class DecoderModel:
@@ -35,10 +38,14 @@ class DecoderModel:
         self.transitions = [build_part("transition", t, self.env) for t in spec.transitions]  # tensors by their full names
         self.entry_caches: list[EntryCache] = []
         for i, e in enumerate(spec.run_order):
-            mixer = self.layers[e.layer].mixer
-            need = mixer.cache_need()
+            block = self.layers[e.layer]
+            mixer = block.mixer
+            # a block that keeps something of its own beside the mixer's cache (a token shift's state) says so itself
+            need = block.cache_need() if hasattr(block, "cache_need") else mixer.cache_need()
             if e.cache_of is None:
                 self.entry_caches.append(EntryCache(i, need))
+            elif isinstance(need, tuple) and any(n is None for n in need) and flat_needs(need):
+                self.entry_caches.append(EntryCache(i, need, shares=self.entry_caches[e.cache_of].owner))
             else:
                 if need is not None:
                     raise ValueError(f"run_order[{i}] reads the cache of entry {e.cache_of}, but its mixer "

@@ -5,6 +5,7 @@ from __future__ import annotations
 import torch
 
 from .. import ops
+from ..config.spec import PartSpec
 from .base import Part, WeightDecl, param, register_part
 
 
@@ -61,6 +62,63 @@ class SwiGLU(Part):
             else:
                 ops.act_mul(act, gate_up, self.activation, stream=ctx.stream)
         return ops.linear(act, self.w_down, stream=ctx.stream, out=ctx.buffer("mlp.down", (t, self.hidden), dt, dev))
+
+
+@register_part("feed_forward", "clamped_glu")
+class ClampedGLU(Part):
+    """down(g * sigmoid(alpha g) * (u + up_shift)) with g = min(gate(x), limit) and u = clamp(up(x), -limit, limit); every
+    projection may have a bias. The gate and up matrices are stacked as in ``swiglu``; their biases are added, and the
+    clamps and the activation computed, in float32 by one kernel behind the product. Parameters: ``hidden``,
+    ``intermediate``, ``limit`` (0: no clamps), optional ``alpha`` (1.702), ``up_shift`` (1.0), ``bias`` (True), ``names``
+    (gate / up / down and gate_bias / up_bias / down_bias -> tensor names)."""
+    shape_static = True
+    NAMES = dict(gate="gate_proj.weight", up="up_proj.weight", down="down_proj.weight", gate_bias="gate_proj.bias",
+                 up_bias="up_proj.bias", down_bias="down_proj.bias")
+
+    def __init__(self, spec, env):
+        super().__init__(spec, env)
+        self.hidden = param(spec, "hidden", int)
+        self.inter = param(spec, "intermediate", int)
+        self.limit = float(spec.get("limit") or 0.0)
+        self.alpha = float(spec.get("alpha", 1.702))
+        self.up_shift = float(spec.get("up_shift", 1.0))
+        self.bias = bool(spec.params.get("bias", True))
+        if self.limit < 0:
+            raise ValueError(f"clamped_glu: limit={self.limit} must not be negative")
+        self.names = {**self.NAMES, **dict(spec.get("names") or {})}
+
+    def weights(self):
+        n = self.names
+        w = {n["gate"]: WeightDecl((self.inter, self.hidden)), n["up"]: WeightDecl((self.inter, self.hidden)),
+             n["down"]: WeightDecl((self.hidden, self.inter))}
+        if self.bias:
+            w.update({n["gate_bias"]: WeightDecl((self.inter,), precision="float32"), n["up_bias"]: WeightDecl((self.inter,), precision="float32"),
+                      n["down_bias"]: WeightDecl((self.hidden,), precision="float32")})
+        return w
+
+    def _stack(self):
+        n = self.names
+        return "gate_up_proj.weight", (n["gate"], n["up"])
+
+    def stacks(self):
+        return dict([self._stack()])
+
+    def bind(self, tensors):
+        n = self.names
+        self.w_gate_up = self.joined(tensors, *self._stack())
+        self.w_down = tensors[n["down"]].contiguous()
+        self.w_in_bias = torch.cat([tensors[n["gate_bias"]].float(), tensors[n["up_bias"]].float()]).contiguous() if self.bias else None
+        self.w_out_bias = tensors[n["down_bias"]].float().contiguous() if self.bias else None
+
+    def forward(self, x, ctx) -> torch.Tensor:
+        t, dt, dev = x.shape[0], self.env.dtype, self.w_down.device
+        gate_up = ops.linear(x, self.w_gate_up, stream=ctx.stream, out=ctx.buffer("mlp.gate_up", (t, 2 * self.inter), dt, dev))
+        act = ctx.buffer("mlp.act", (t, self.inter), dt, dev)
+        ops.clamped_glu(act, gate_up, self.w_in_bias, self.limit, self.alpha, self.up_shift, stream=ctx.stream)
+        out = ops.linear(act, self.w_down, stream=ctx.stream, out=ctx.buffer("mlp.down", (t, self.hidden), dt, dev))
+        if self.w_out_bias is not None:
+            ops.sum_bias(out, out, None, self.w_out_bias, stream=ctx.stream)
+        return out
 
 
 @register_part("feed_forward", "dense_mlp")
@@ -129,10 +187,16 @@ class RoutedExperts(Part):
     Parameters: ``hidden``, ``intermediate``, ``experts``, ``top``; optional ``identity`` (0), ``group_count`` (1),
     ``group_keep`` (1), ``weight_scale`` (1.0), ``renormalize`` (False), ``correction`` (True: a tensor of that name is
     added to the scores for the choice), ``activation`` (``silu`` or ``gelu_tanh``), ``score`` (``softmax``), ``names``
-    (router, correction, gate, up, down -> tensor names; ``expert``: the prefix of expert e with ``{}`` for e)."""
+    (router, correction, gate, up, down -> tensor names; ``expert``: the prefix of expert e with ``{}`` for e).
+
+    ``router_bias`` (True: a tensor [outputs] of that name is added to the logits themselves; with ``renormalize`` and no
+    correction the weights are then the softmax over the chosen logits alone). ``shared`` (an intermediate size): one
+    more gated feed-forward of the experts' form (a ``swiglu`` part under the prefix ``shared``) that every token uses;
+    its output is added times sigmoid(w_sg . x), one number per token (tensor ``shared_gate`` [1, hidden], float32,
+    computed by the router's kernel from the same input), or unweighted with ``shared_gated`` False."""
     shape_static = True
     NAMES = dict(router="router.weight", correction="router.correction", expert="experts.{}.", gate="gate_proj.weight",
-                 up="up_proj.weight", down="down_proj.weight")
+                 up="up_proj.weight", down="down_proj.weight", router_bias="router.bias", shared="shared.", shared_gate="shared.gate")
 
     def __init__(self, spec, env):
         super().__init__(spec, env)
@@ -159,6 +223,18 @@ class RoutedExperts(Part):
             raise ValueError(f"routed_experts: {self.outputs} router outputs in {self.group_count} groups of which {self.group_keep} are "
                              f"kept cannot give {self.top} choices")
         self.names = {**self.NAMES, **dict(spec.get("names") or {})}
+        self.has_router_bias = bool(spec.get("router_bias", False))
+        self.shared_inter = int(spec.get("shared") or 0)
+        self.shared_gated = bool(spec.params.get("shared_gated", True)) and self.shared_inter > 0
+        self.shared = None
+        if self.shared_inter:
+            n = self.names
+            self.shared = SwiGLU(PartSpec("swiglu", dict(hidden=self.hidden, intermediate=self.shared_inter, activation=self.activation,
+                                                         names=dict(gate=n["gate"], up=n["up"], down=n["down"]))), env)
+        self.w_router_bias = self.w_shared_gate = None
+
+    def sub_parts(self):
+        return {self.names["shared"]: self.shared} if self.shared is not None else {}
 
     def _expert(self, e: int, which: str) -> str:
         return self.names["expert"].format(e) + self.names[which]
@@ -168,6 +244,10 @@ class RoutedExperts(Part):
         w = {n["router"]: WeightDecl((self.outputs, self.hidden), precision="float32")}
         if self.has_correction:
             w[n["correction"]] = WeightDecl((self.outputs,), precision="float32")
+        if self.has_router_bias:
+            w[n["router_bias"]] = WeightDecl((self.outputs,), precision="float32")
+        if self.shared_gated:
+            w[n["shared_gate"]] = WeightDecl((1, self.hidden), precision="float32")
         for e in range(self.experts):
             w[self._expert(e, "gate")] = WeightDecl((self.inter, self.hidden))
             w[self._expert(e, "up")] = WeightDecl((self.inter, self.hidden))
@@ -182,6 +262,8 @@ class RoutedExperts(Part):
         n, st = self.names, self.stacks()
         self.w_router = tensors[n["router"]].float().contiguous()
         self.w_correction = tensors[n["correction"]].float().contiguous() if self.has_correction else None
+        self.w_router_bias = tensors[n["router_bias"]].float().contiguous() if self.has_router_bias else None
+        self.w_shared_gate = tensors[n["shared_gate"]].float().reshape(-1).contiguous() if self.shared_gated else None
         self.w_gate_up = self.joined(tensors, "experts.gate_up", st["experts.gate_up"]).view(self.experts, 2 * self.inter, self.hidden)
         self.w_down = self.joined(tensors, "experts.down", st["experts.down"]).view(self.experts, self.hidden, self.inter)
 
@@ -190,8 +272,10 @@ class RoutedExperts(Part):
         t, dev = x.shape[0], self.w_down.device
         idx = ctx.buffer("moe.idx", (t, self.top), torch.int32, dev)
         wgt = ctx.buffer("moe.wgt", (t, self.top), torch.float32, dev)
+        gate = ctx.buffer("moe.shared_gate", (t,), torch.float32, dev) if self.shared_gated else None
         ops.experts.expert_route(idx, wgt, x, self.w_router, self.w_correction, self.top, self.group_count, self.group_keep,
-                                 self.weight_scale, self.renormalize, stream=ctx.stream)
+                                 self.weight_scale, self.renormalize, stream=ctx.stream, logit_bias=self.w_router_bias,
+                                 gate_w=self.w_shared_gate, gate_out=gate)
         return idx, wgt
 
     def forward(self, x, ctx) -> torch.Tensor:
@@ -218,5 +302,7 @@ class RoutedExperts(Part):
             ops.experts.expert_gate_up(act, x, self.w_gate_up, perm, self.top, tiles, meta, offsets, self.activation, stream=ctx.stream)
             ops.experts.expert_down(y, act, self.w_down, tiles, meta, offsets, stream=ctx.stream)
         out = ctx.buffer("moe.out", (t, self.hidden), dt, dev)
-        ops.experts.expert_combine(out, y, x, idx, wgt, pos, self.experts, stream=ctx.stream)
+        shared = self.shared.forward(x, ctx) if self.shared is not None else None
+        gate = ctx.buffer("moe.shared_gate", (t,), torch.float32, dev) if self.shared_gated else None  # written by the router's kernel
+        ops.experts.expert_combine(out, y, x, idx, wgt, pos, self.experts, stream=ctx.stream, shared=shared, shared_gate=gate)
         return out
