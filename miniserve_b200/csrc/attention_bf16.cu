@@ -104,7 +104,13 @@ struct AttnExtras {
   float cap_log2;            // cap * log2(e)
   float cap_inv;             // scale / cap; 0: no cap
   int chunk;                 // 0: no block mask
+  const float* dist_r1;      // [nq] or null: r1_h * ln(1 + r2_h * (i - j)) is taken off the score of query i and key j
+  const float* dist_r2;      // [nq]
+  int keep_first;            // the first keep_first keys of a request stay visible behind the window; 0: none
 };
+
+// the distance bias of one (query, key) pair in the kernels' units (powers of two): r1 ln(x) log2(e) = r1 log2(x)
+__device__ __forceinline__ float distance_bias(float r1, float r2, int distance) { return r1 * __log2f(fmaf(r2, (float)distance, 1.0f)); }
 
 // tanh(y) = 1 - 2 / (1 + 2^(2 y log2 e)): two fast special-function operations, absolute error about 1e-6 (times the
 // cap, far below the bfloat16 rounding of the probabilities)
@@ -119,12 +125,16 @@ __device__ __forceinline__ float sink_term(int sink, const AttnExtras& ex, int h
   return exp2f((ex.sink_values ? ex.sink_values[head] * LOG2E : 0.f) - m);
 }
 
-static AttnExtras make_extras(const float* sink_values, float scale, float softcap, int chunk) {
+static AttnExtras make_extras(const float* sink_values, float scale, float softcap, int chunk, const float* dist_r1 = nullptr,
+                              const float* dist_r2 = nullptr, int keep_first = 0) {
   AttnExtras ex;
   ex.sink_values = sink_values;
   ex.cap_log2 = softcap * LOG2E;
   ex.cap_inv = softcap > 0.f ? scale / softcap : 0.f;
   ex.chunk = chunk;
+  ex.dist_r1 = dist_r2 ? dist_r1 : nullptr;
+  ex.dist_r2 = dist_r2;
+  ex.keep_first = keep_first > 0 ? keep_first : 0;
   return ex;
 }
 
@@ -159,6 +169,15 @@ attn_prefill_kernel(__nv_bfloat16* __restrict__ out, const __nv_bfloat16* __rest
   int lo = window > 0 ? max(0, q_first - window + 1) : 0;
   if (ex.chunk > 0) lo = max(lo, (q_first / ex.chunk) * ex.chunk);  // the tile's first query sees furthest back
   const int tile_begin = lo / PF_BN, tile_end = (hi + PF_BN - 1) / PF_BN;
+  // Kept first keys: their tiles (those wholly before the window's first tile) are walked first. The walk runs over
+  // virtual tiles [walk_begin, tile_end); the first `kept_tiles` of them are tiles 0, 1, ... of the request. With kept
+  // keys the cache gives no page back, so every key below `hi` may be loaded and the mask alone decides.
+  const int keep = ex.keep_first;
+  const int kept_tiles = keep > 0 ? min((keep + PF_BN - 1) / PF_BN, tile_begin) : 0;
+  const int walk_begin = tile_begin - kept_tiles;
+  const int lo_load = keep > 0 ? 0 : lo;
+  const float r1 = ex.dist_r1 ? ex.dist_r1[head] : 0.f, r2 = ex.dist_r1 ? ex.dist_r2[head] : 0.f;
+#define MS_PF_TILE(wt) ((wt) < tile_begin ? (wt) - walk_begin : (wt))
 
   // q tile
   for (int idx = tid; idx < PF_BM * CHUNKS; idx += PF_THREADS) {
@@ -167,7 +186,7 @@ attn_prefill_kernel(__nv_bfloat16* __restrict__ out, const __nv_bfloat16* __rest
     const __nv_bfloat16* src = q + ((size_t)(tok0 + (valid ? m0 + row : 0)) * nq + head) * D + chunk * 8;
     cp_async16(qs + row * DPAD + chunk * 8, src, valid);
   }
-  load_kv_tile<PF_BN, PF_THREADS>(ks, vs, kv, tile_begin * PF_BN, lo, hi, tid);
+  load_kv_tile<PF_BN, PF_THREADS>(ks, vs, kv, MS_PF_TILE(walk_begin) * PF_BN, lo_load, hi, tid);
   cp_async_commit();
 
   uint32_t qf[Q_IN_REGS ? KSTEPS : 1][4];
@@ -178,15 +197,16 @@ attn_prefill_kernel(__nv_bfloat16* __restrict__ out, const __nv_bfloat16* __rest
   const int qpos[2] = {start + m0 + warp * 16 + g, start + m0 + warp * 16 + g + 8};
   const int block_lo[2] = {ex.chunk > 0 ? (qpos[0] / ex.chunk) * ex.chunk : 0, ex.chunk > 0 ? (qpos[1] / ex.chunk) * ex.chunk : 0};
 
-  for (int tile = tile_begin; tile < tile_end; ++tile) {
-    const int stage = (tile - tile_begin) & 1;
-    if (tile + 1 < tile_end)
+  for (int wt = walk_begin; wt < tile_end; ++wt) {
+    const int tile = MS_PF_TILE(wt);
+    const int stage = (wt - walk_begin) & 1;
+    if (wt + 1 < tile_end)
       load_kv_tile<PF_BN, PF_THREADS>(ks + (stage ^ 1) * PF_BN * DPAD, vs + (stage ^ 1) * PF_BN * DPAD, kv,
-                                      (tile + 1) * PF_BN, lo, hi, tid);
+                                      MS_PF_TILE(wt + 1) * PF_BN, lo_load, hi, tid);
     cp_async_commit();
     cp_async_wait<1>();
     __syncthreads();
-    if (Q_IN_REGS && tile == tile_begin) {
+    if (Q_IN_REGS && wt == walk_begin) {
 #pragma unroll
       for (int kk = 0; kk < (Q_IN_REGS ? KSTEPS : 1); ++kk)
         ldmatrix_x4(qf[kk], qs + (warp * 16 + (lane & 15)) * DPAD + kk * 16 + (lane >> 4) * 8);
@@ -222,8 +242,8 @@ attn_prefill_kernel(__nv_bfloat16* __restrict__ out, const __nv_bfloat16* __rest
       for (int e = 0; e < 4; ++e) {
         const int key = key_base + nt * 8 + (e & 1);
         const int qp = qpos[e >> 1];
-        const bool ok = key <= qp && key >= lo && (window <= 0 || key > qp - window) && key >= block_lo[e >> 1];
-        s[nt][e] = ok ? shaped_score(s[nt][e], scale_log2, ex) : -INFINITY;
+        const bool ok = key <= qp && ((key >= lo && (window <= 0 || key > qp - window)) || key < keep) && key >= block_lo[e >> 1];
+        s[nt][e] = ok ? shaped_score(s[nt][e], scale_log2, ex) - (ex.dist_r1 ? distance_bias(r1, r2, qp - key) : 0.f) : -INFINITY;
         m_new[e >> 1] = fmaxf(m_new[e >> 1], s[nt][e]);
       }
     float alpha[2], m_use[2];
@@ -279,6 +299,7 @@ attn_prefill_kernel(__nv_bfloat16* __restrict__ out, const __nv_bfloat16* __rest
     for (int dt = 0; dt < DTILES; ++dt)
       *reinterpret_cast<uint32_t*>(dst + dt * 8) = pack_bf16(o[dt][2 * i] * inv, o[dt][2 * i + 1] * inv);
   }
+#undef MS_PF_TILE
 }
 
 // ------------------------------------------------------------------ decode: split-K over the keys
@@ -320,8 +341,15 @@ attn_decode_kernel(__nv_bfloat16* __restrict__ out, float* __restrict__ part_o, 
   if (ex.chunk > 0) lo = max(lo, ((kv_len - 1) / ex.chunk) * ex.chunk);  // the one query sits at position kv_len - 1
   // the key range of this split, in whole slices
   const int first_slice = lo / DC_SLICE, end_slice = (kv_len + DC_SLICE - 1) / DC_SLICE;
-  const int per_split = (end_slice - first_slice + num_splits - 1) / num_splits;
-  const int s_begin = first_slice + split * per_split, s_end = min(end_slice, s_begin + per_split);
+  // Kept first keys: their slices (those wholly before the window's first slice) come first in the walk over virtual
+  // slices [walk_first, end_slice); with kept keys no page was given back, so the mask alone decides what counts.
+  const int keep = ex.keep_first;
+  const int kept_slices = keep > 0 ? min((keep + DC_SLICE - 1) / DC_SLICE, first_slice) : 0;
+  const int walk_first = first_slice - kept_slices;
+  const int lo_load = keep > 0 ? 0 : lo;
+#define MS_DC_SLICE(sl) ((sl) < first_slice ? (sl) - walk_first : (sl))
+  const int per_split = (end_slice - walk_first + num_splits - 1) / num_splits;
+  const int s_begin = walk_first + split * per_split, s_end = min(end_slice, s_begin + per_split);
 
   extern __shared__ __align__(16) unsigned char smem_raw[];
   __nv_bfloat16* qs = reinterpret_cast<__nv_bfloat16*>(smem_raw);
@@ -340,7 +368,7 @@ attn_decode_kernel(__nv_bfloat16* __restrict__ out, float* __restrict__ part_o, 
   auto issue = [&](int i) {
     if (i < my_count) {
       __nv_bfloat16* st = pipe + (i % DC_STAGES) * DecodeSmem::stage_elems;
-      const int key0 = (my_first + i * DC_WARPS) * DC_SLICE;
+      const int key0 = MS_DC_SLICE(my_first + i * DC_WARPS) * DC_SLICE;
       if (page_shift >= 4) {
         // pages of at least 16 tokens: the whole slice lies in one page, one lookup per slice
         const int page = kv.pages[key0 >> page_shift];
@@ -348,13 +376,13 @@ attn_decode_kernel(__nv_bfloat16* __restrict__ out, float* __restrict__ part_o, 
 #pragma unroll
         for (int it = 0; it < DC_SLICE * CHUNKS / 32; ++it) {
           const int idx = it * 32 + lane, row = idx / CHUNKS, chunk = idx - row * CHUNKS;
-          const bool valid = key0 + row >= lo && key0 + row < kv_len;
+          const bool valid = key0 + row >= lo_load && key0 + row < kv_len;
           const size_t off = valid ? base + row * D + chunk * 8 : 0;
           cp_async16(st + row * DPAD + chunk * 8, kv.k + off, valid);
           cp_async16(st + (DC_SLICE + row) * DPAD + chunk * 8, kv.v + off, valid);
         }
       } else {
-        load_kv_tile<DC_SLICE, 32>(st, st + DC_SLICE * DPAD, kv, key0, lo, kv_len, lane);
+        load_kv_tile<DC_SLICE, 32>(st, st + DC_SLICE * DPAD, kv, key0, lo_load, kv_len, lane);
       }
     }
     cp_async_commit();
@@ -364,7 +392,7 @@ attn_decode_kernel(__nv_bfloat16* __restrict__ out, float* __restrict__ part_o, 
   const int newest_slice = (kv_len - 1) / DC_SLICE;
   int issued = 0;
   for (; issued < DC_STAGES - 1; ++issued) {
-    if (issued < my_count && my_first + issued * DC_WARPS >= newest_slice) break;
+    if (issued < my_count && MS_DC_SLICE(my_first + issued * DC_WARPS) >= newest_slice) break;
     issue(issued);
   }
   pdl_wait();
@@ -383,6 +411,15 @@ attn_decode_kernel(__nv_bfloat16* __restrict__ out, float* __restrict__ part_o, 
       ldmatrix_x4(qf[kk], qs + (lane & 15) * DPAD + kk * 16 + (lane >> 4) * 8);
   }
 
+  float dr1[2] = {0.f, 0.f}, dr2[2] = {0.f, 0.f};
+  if (ex.dist_r1) {
+#pragma unroll
+    for (int j = 0; j < 2; ++j) {
+      const int hd = min(head0 + g + 8 * j, nq - 1);  // (rows beyond this CTA's heads hold zero queries and are not stored)
+      dr1[j] = ex.dist_r1[hd];
+      dr2[j] = ex.dist_r2[hd];
+    }
+  }
   for (int i = 0; i < my_count; ++i) {
     issue(i + DC_STAGES - 1);
     cp_async_wait<DC_STAGES - 1>();
@@ -402,15 +439,17 @@ attn_decode_kernel(__nv_bfloat16* __restrict__ out, float* __restrict__ part_o, 
       mma_bf16(s[0], a, b[0], b[1]);
       mma_bf16(s[1], a, b[2], b[3]);
     }
-    const int key_base = (my_first + i * DC_WARPS) * DC_SLICE + 2 * t;
+    const int key_base = MS_DC_SLICE(my_first + i * DC_WARPS) * DC_SLICE + 2 * t;
     float m_new[2] = {m_run[0], m_run[1]};
 #pragma unroll
     for (int nt = 0; nt < 2; ++nt)
 #pragma unroll
       for (int e = 0; e < 4; ++e) {
         const int key = key_base + nt * 8 + (e & 1);
-        const bool ok = key >= lo && key < kv_len;
-        s[nt][e] = ok ? shaped_score(s[nt][e], scale_log2, ex) : -INFINITY;
+        const bool ok = (key >= lo || key < keep) && key < kv_len;
+        // rows of the tile are query heads (g and g + 8 of this CTA's sixteen), all at position kv_len - 1
+        s[nt][e] = ok ? shaped_score(s[nt][e], scale_log2, ex) - (ex.dist_r1 ? distance_bias(dr1[e >> 1], dr2[e >> 1], kv_len - 1 - key) : 0.f)
+                      : -INFINITY;
         m_new[e >> 1] = fmaxf(m_new[e >> 1], s[nt][e]);
       }
     float alpha[2], m_use[2], row_sum[2] = {0.f, 0.f};
@@ -597,6 +636,7 @@ attn_decode_kernel(__nv_bfloat16* __restrict__ out, float* __restrict__ part_o, 
     l += sink_term(sink, ex, head0 + row, m);
     out[item * D + c] = __float2bfloat16_rn(acc / l);
   }
+#undef MS_DC_SLICE
 }
 
 // out[r, head] = sum_s w_s O_s / sum_s w_s l_s with w_s = 2^(m_s - max m)
@@ -642,7 +682,8 @@ static int shift_of(int page_size) {
 MS_EXPORT int MS_ATTN_FN(prefill)(void* out, const void* q, const void* k_pool, const void* v_pool, const int* cu_q,
                                   const int* q_start, const int* page_indptr, const int* page_indices, int num_rows,
                                   int max_q_len, int nq, int nkv, float scale, int window, int sink, int page_size,
-                                  cudaStream_t stream, const float* sink_values, float softcap, int chunk) {
+                                  cudaStream_t stream, const float* sink_values, float softcap, int chunk, const float* dist_r1,
+                                  const float* dist_r2, int keep_first) {
   if (num_rows == 0) return 0;
   MS_CHECK_ARG(softcap >= 0.f && chunk >= 0, "attention: softcap=%g and chunk=%d must not be negative", softcap, chunk);
   MS_CHECK_ARG(nq > 0 && nkv > 0 && nq % nkv == 0, "attention: %d query heads are not a multiple of %d kv heads", nq, nkv);
@@ -661,7 +702,7 @@ MS_EXPORT int MS_ATTN_FN(prefill)(void* out, const void* q, const void* k_pool, 
   MS_LAUNCH(attn_prefill_kernel, grid, PF_THREADS, smem, stream,
       (__nv_bfloat16*)out, (const __nv_bfloat16*)q, (const __nv_bfloat16*)k_pool, (const __nv_bfloat16*)v_pool, cu_q,
       q_start, page_indptr, page_indices, nq, nkv, scale * LOG2E, window, sink || sink_values != nullptr, shift_of(page_size),
-      make_extras(sink_values, scale, softcap, chunk));
+      make_extras(sink_values, scale, softcap, chunk, dist_r1, dist_r2, keep_first));
   MS_CHECK_LAUNCH();
   return 0;
 }
@@ -670,7 +711,8 @@ MS_EXPORT int MS_ATTN_FN(decode_fused)(void* out, void* part_o, void* part_ml, i
                                        const void* k_pool, const void* v_pool, const int* kv_len,
                                        const int* page_indptr, const int* page_indices, int num_rows, int nq, int nkv,
                                        float scale, int window, int sink, int page_size, int num_splits, cudaStream_t stream,
-                                       const float* sink_values, float softcap, int chunk);
+                                       const float* sink_values, float softcap, int chunk, const float* dist_r1, const float* dist_r2,
+                                       int keep_first);
 
 // The decode kernel's shared-memory attribute belongs to a device: set once for each.
 static int configure_decode() {
@@ -691,7 +733,7 @@ MS_EXPORT int MS_ATTN_FN(decode)(void* out, void* part_o, void* part_ml, const v
                                  const int* page_indices, int num_rows, int nq, int nkv, float scale, int window, int sink,
                                  int page_size, int num_splits, cudaStream_t stream) {
   return MS_ATTN_FN(decode_fused)(out, part_o, part_ml, nullptr, q, k_pool, v_pool, kv_len, page_indptr, page_indices,
-                                  num_rows, nq, nkv, scale, window, sink, page_size, num_splits, stream, nullptr, 0.f, 0);
+                                  num_rows, nq, nkv, scale, window, sink, page_size, num_splits, stream, nullptr, 0.f, 0, nullptr, nullptr, 0);
 }
 
 // As above; with `counters` (num_rows * kv_heads * ceil(group / 16) ints, zero before the first
@@ -701,11 +743,12 @@ MS_EXPORT int MS_ATTN_FN(decode_fused)(void* out, void* part_o, void* part_ml, i
                                        const void* k_pool, const void* v_pool, const int* kv_len,
                                        const int* page_indptr, const int* page_indices, int num_rows, int nq, int nkv,
                                        float scale, int window, int sink, int page_size, int num_splits, cudaStream_t stream,
-                                       const float* sink_values, float softcap, int chunk) {
+                                       const float* sink_values, float softcap, int chunk, const float* dist_r1, const float* dist_r2,
+                                       int keep_first) {
   if (num_rows == 0) return 0;
   MS_CHECK_ARG(softcap >= 0.f && chunk >= 0, "attention: softcap=%g and chunk=%d must not be negative", softcap, chunk);
   sink = sink || sink_values != nullptr;
-  const AttnExtras ex = make_extras(sink_values, scale, softcap, chunk);
+  const AttnExtras ex = make_extras(sink_values, scale, softcap, chunk, dist_r1, dist_r2, keep_first);
   MS_CHECK_ARG(nq > 0 && nkv > 0 && nq % nkv == 0, "attention: %d query heads are not a multiple of %d kv heads", nq, nkv);
   MS_CHECK_ARG(page_size > 0 && (page_size & (page_size - 1)) == 0, "attention: page_size=%d must be a power of two", page_size);
   MS_CHECK_ARG(num_splits >= 1 && num_splits <= 65535, "attention: bad split count %d", num_splits);
@@ -731,11 +774,12 @@ MS_EXPORT int MS_ATTN_FN(decode_fused)(void* out, void* part_o, void* part_ml, i
 MS_EXPORT int MS_ATTN_FN(decode_cluster)(void* out, const void* q, const void* k_pool, const void* v_pool, const int* kv_len,
                                          const int* page_indptr, const int* page_indices, int num_rows, int nq, int nkv,
                                          float scale, int window, int sink, int page_size, int num_splits, cudaStream_t stream,
-                                         const float* sink_values, float softcap, int chunk) {
+                                         const float* sink_values, float softcap, int chunk, const float* dist_r1,
+                                         const float* dist_r2, int keep_first) {
   if (num_rows == 0) return 0;
   MS_CHECK_ARG(softcap >= 0.f && chunk >= 0, "attention: softcap=%g and chunk=%d must not be negative", softcap, chunk);
   sink = sink || sink_values != nullptr;
-  const AttnExtras ex = make_extras(sink_values, scale, softcap, chunk);
+  const AttnExtras ex = make_extras(sink_values, scale, softcap, chunk, dist_r1, dist_r2, keep_first);
   MS_CHECK_ARG(nq > 0 && nkv > 0 && nq % nkv == 0, "attention: %d query heads are not a multiple of %d kv heads", nq, nkv);
   MS_CHECK_ARG(page_size > 0 && (page_size & (page_size - 1)) == 0, "attention: page_size=%d must be a power of two", page_size);
   MS_CHECK_ARG(num_splits >= 2 && num_splits <= 8, "attention: a cluster takes 2 to 8 splits, not %d", num_splits);

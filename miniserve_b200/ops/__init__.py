@@ -541,13 +541,14 @@ def attention(out: torch.Tensor, q: torch.Tensor, k_pool: torch.Tensor, v_pool: 
     from . import attention_bf16
 
     extras = extras if extras is not None and extras.any else None
-    if extras is not None and (extras.positional or not (q.dtype == torch.bfloat16 and attention_bf16.takes_extras(q.shape[2], k_pool.shape[2]))):
+    if extras is not None and not (q.dtype == torch.bfloat16 and attention_bf16.takes_extras(q.shape[2], k_pool.shape[2])):
         attention_rowwise(out, q, k_pool, v_pool, ctx.positions, ctx.row_of_token, ctx.page_indptr[group],
                           ctx.page_indices[group], scale, window, ctx.status, stream=ctx.stream, sink=sink, extras=extras)
         return
     recorder = getattr(ctx, "recorder", None)
     split_ok = q.dtype == torch.bfloat16 and attention_bf16.supports(q.shape[2], k_pool.shape[2])
-    tc_ok = q.dtype == torch.bfloat16 and attention_tc_ok(q, k_pool)
+    # (a distance bias and kept first keys are in the mma.sync kernels and the row-wise kernel, not in the tcgen05 kernel)
+    tc_ok = q.dtype == torch.bfloat16 and not (extras is not None and extras.positional) and attention_tc_ok(q, k_pool)
     if recorder is not None and (tc_ok or split_ok):
         # The pass is being captured into CUDA graphs. Which tensor-core kernels run here, their grids and
         # their key splits depend on each row's length and start, which a graph cannot hold.

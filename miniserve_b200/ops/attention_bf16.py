@@ -28,15 +28,17 @@ def supports(head_dim: int, page_size: int) -> bool:
 
 
 def takes_extras(head_dim: int, page_size: int) -> bool:
-    """Whether these kernels take learned sink scores, a cap on the scores and a mask by blocks of positions."""
+    """Whether these kernels take learned sink scores, a cap on the scores, a mask by blocks of positions, a distance
+    bias and kept first keys."""
     return supports(head_dim, page_size)
 
 
 def _extras_args(extras) -> tuple:
     if extras is None:
-        return (None, 0.0, 0)
-    sv = extras.sink_values
-    return (None if sv is None else sv.data_ptr(), float(extras.softcap or 0.0), int(extras.chunk or 0))
+        return (None, 0.0, 0, None, None, 0)
+    sv, r1, r2 = extras.sink_values, extras.dist_r1, extras.dist_r2
+    return (None if sv is None else sv.data_ptr(), float(extras.softcap or 0.0), int(extras.chunk or 0),
+            None if r1 is None else r1.data_ptr(), None if r2 is None else r2.data_ptr(), int(extras.keep_first or 0))
 
 
 def module_for(head_dim: int) -> build.Module:
@@ -52,10 +54,10 @@ def _lib(head_dim: int):
     fns = {}
     for name, args, res in (
         ("last_error", [], c_char_p),
-        ("prefill", [_p] * 8 + [_i, _i, _i, _i, _f, _i, _i, _i, _p, _p, _f, _i], c_int),
+        ("prefill", [_p] * 8 + [_i, _i, _i, _i, _f, _i, _i, _i, _p, _p, _f, _i, _p, _p, _i], c_int),
         ("decode", [_p] * 9 + [_i, _i, _i, _f, _i, _i, _i, _i, _p], c_int),
-        ("decode_fused", [_p] * 10 + [_i, _i, _i, _f, _i, _i, _i, _i, _p, _p, _f, _i], c_int),
-        ("decode_cluster", [_p] * 7 + [_i, _i, _i, _f, _i, _i, _i, _i, _p, _p, _f, _i], c_int),
+        ("decode_fused", [_p] * 10 + [_i, _i, _i, _f, _i, _i, _i, _i, _p, _p, _f, _i, _p, _p, _i], c_int),
+        ("decode_cluster", [_p] * 7 + [_i, _i, _i, _f, _i, _i, _i, _i, _p, _p, _f, _i, _p, _p, _i], c_int),
         ("decode_clusters_resident", [_i, ctypes.POINTER(c_int)], c_int),
     ):
         fn = getattr(lib, pre + name)
