@@ -23,7 +23,9 @@ Qwen3-1.7B) beside the Qwen3 model of the same width, depth, feed-forward size a
 2,048-token prompt step and decode steps at batch 8 behind 2,048 tokens; ``--kernels`` adds the device
 time per kernel of both steps. ``--config mugipel`` does the same for the Mugipel design (attention layers
 with capped scores, a block mask and learned sinks in turn with latent-attention layers, the last stretch of
-layers run twice). ``--config rofozen`` does the same for the Rofozen design (state-space layers with one decay
+layers run twice). ``--config kovusun`` does the same for the Kovusun design (windowed attention with a distance bias,
+kept first keys or a sink, token shift, layer norms, dense and routed feed-forwards with a shared expert), beside Qwen3, Mugipel
+and Rofozen. ``--config rofozen`` does the same for the Rofozen design (state-space layers with one decay
 per head, every fourth layer latent attention with a rotated key part, a window and learned sinks; routed experts
 in every other layer), beside Qwen3 and beside Fekulix, the framework's other design with recurrent layers.
 """
@@ -390,6 +392,28 @@ def rofozen_config(width: int, ff: int, runs: int, vocab: int, heads: int, kv_he
     return {"architecture": "Rofozen", "width": width, "vocab": vocab, "norm": {"eps": 1e-6}, "layers": layers}
 
 
+def kovusun_config(width: int, ff: int, runs: int, vocab: int, heads: int, kv_heads: int) -> dict:
+    """A Kovusun model at a real model's layer sizes: heads of 128 (the Qwen3 model's head counts), windows of 1,024, in
+    turns of four layers: attention with biases and a distance bias; rotary attention with a temperature per head and 4
+    kept first keys; attention that reads the first layer's keys and values; attention with a sink and a gate per head.
+    The feed-forward is dense with clamps in even layers, and in odd ones 16 experts of ff / 4 of which a token uses 3
+    beside a shared expert of ff / 4 (the products of a token equal the dense layer's)."""
+    base = {"dim": 128, "heads": heads, "kv_heads": kv_heads, "mask": {"size": 1024}, "scale": 128 ** -0.5, "vdim": 128}
+    dense = {"ff": ff, "kind": "dense", "limit": 7.0}
+    moe = {"kind": "moe", "expert": {"ff": ff // 4}, "router": {"experts": 16, "top": 3}, "shared": {"ff": ff // 4}}
+    layers = []
+    for i in range(runs):
+        kind = ("attention", "attention_3", "attention", "attention_2")[i % 4]
+        mixer = {k: (dict(v) if isinstance(v, dict) else v) for k, v in base.items()}
+        if i % 4 == 1:
+            mixer["mask"]["keep_first"] = 4
+            mixer["rot"] = {"base": 1e6, "dims": 128}
+        if i % 4 == 2:
+            mixer["kv_from"] = i - 2
+        layers.append({"type": kind, "mixer": mixer, "mlp": dict(moe if i % 2 else dense)})
+    return {"architecture": "Kovusun", "width": width, "vocab": vocab, "norm": {"eps": 1e-5}, "layers": layers}
+
+
 def bytes_per_step_of_weights(model) -> int:
     """Bytes of weights a step reads: every run of a layer reads that layer's tensors (a layer that runs twice
     counts twice), plus the norm before the head, the head and the parts between layers."""
@@ -446,7 +470,7 @@ def run_fekulix(args, design: str = "fekulix") -> dict:
     from miniserve_b200.engine.step import StepRow
 
     peaks = load_peaks()
-    make = {"fekulix": fekulix_config, "mugipel": mugipel_config, "rofozen": rofozen_config}[design]
+    make = {"fekulix": fekulix_config, "mugipel": mugipel_config, "rofozen": rofozen_config, "kovusun": kovusun_config}[design]
     out = {"impl": "ours", "config": design, "dtype": "bf16", "data": "synthetic (random-init weights, uniform token ids)",
            "batch": args.batch, "context": CONTEXT, "prefill_tokens": PREFILL_TOKENS, "peaks": peaks["source"], "sizes": {}}
     steps = min(args.steps, 64)
@@ -461,6 +485,10 @@ def run_fekulix(args, design: str = "fekulix") -> dict:
         if design == "rofozen":  # the framework's other design with recurrent layers, at the same sizes
             beside.append(("fekulix", fekulix_config(q["hidden_size"], q["intermediate_size"], q["num_hidden_layers"], q["vocab_size"],
                                                      q["num_attention_heads"], q["num_key_value_heads"])))
+        if design == "kovusun":  # the framework's designs that are closest: windowed attention with extras, and routed experts
+            args_of = (q["hidden_size"], q["intermediate_size"], q["num_hidden_layers"], q["vocab_size"], q["num_attention_heads"],
+                       q["num_key_value_heads"])
+            beside += [("mugipel", mugipel_config(*args_of)), ("rofozen", rofozen_config(*args_of))]
         for name, raw in [(design, f)] + beside:
             llm = LLM(random=raw, weights_seed=0, dtype="bfloat16", kv_pool_tokens=10 * (CONTEXT + steps + 64) + 4096, page_size=16,
                       max_running=16, chunked_prefill_size=2048, cuda_graph=not args.no_graph)
@@ -671,10 +699,10 @@ def main() -> int:
     ap.add_argument("--no-graph", action="store_true", help="run decode steps without CUDA graphs")
     ap.add_argument("--profile-range", action="store_true",
                     help="bracket the timed steps with cudaProfilerStart/Stop (for ncu --profile-from-start off)")
-    ap.add_argument("--config", choices=["0.6b", "8b", "32b", "fekulix", "mugipel", "rofozen"], default="0.6b",
+    ap.add_argument("--config", choices=["0.6b", "8b", "32b", "fekulix", "mugipel", "rofozen", "kovusun"], default="0.6b",
                     help="0.6b: the benchmark line; 8b, 32b: the larger workloads through Engine.generate (a line of their own); "
-                         "fekulix, mugipel, rofozen: prefill and decode of that design beside Qwen3 at equal sizes (a line of its own)")
-    ap.add_argument("--kernels", action="store_true", help="with --config fekulix, mugipel or rofozen: also device time per kernel of a prompt step and a decode step")
+                         "fekulix, mugipel, rofozen, kovusun: prefill and decode of that design beside Qwen3 at equal sizes (a line of its own)")
+    ap.add_argument("--kernels", action="store_true", help="with --config fekulix, mugipel, rofozen or kovusun: also device time per kernel of a prompt step and a decode step")
     ap.add_argument("--only", choices=["all", "decode", "prefill"], default="all",
                     help="measure only the decode steps or only the prefill (for profiling); the line then lacks the other parts")
     args = ap.parse_args()
@@ -687,7 +715,7 @@ def main() -> int:
         args.warmup = 3
     global PROFILE_RANGE
     PROFILE_RANGE = args.profile_range
-    if args.config in ("fekulix", "mugipel", "rofozen") and args.impl == "ours":
+    if args.config in ("fekulix", "mugipel", "rofozen", "kovusun") and args.impl == "ours":
         result = run_fekulix(args, args.config)
     elif args.config != "0.6b" and args.impl == "ours":
         result = run_workload(args)

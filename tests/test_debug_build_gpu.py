@@ -54,7 +54,7 @@ SCRIPT = textwrap.dedent("""
         native.kernel_check(k.ms_attention_rowwise(
             out.data_ptr(), q.data_ptr(), k_pool.data_ptr(), v_pool.data_ptr(), positions.data_ptr(), row_of.data_ptr(),
             indptr.data_ptr(), indices.data_ptr(), 2, nq, nkv, d, 0.2, 0, 0, page, told, status.data_ptr(), 0,
-            torch.cuda.current_stream().cuda_stream, None, 0.0, 0))
+            torch.cuda.current_stream().cuda_stream, None, 0.0, 0, None, None, 0))
         torch.cuda.synchronize()
 
     read(torch.tensor([1, 2, 11], **i32))
