@@ -192,7 +192,15 @@ struct AtExtras {
   const float* sink_values;  // [nq] or null
   float cap_raw;             // cap / scale
   float cap_c2;              // 2 log2(e) scale / cap; 0: no cap
+  // a distance bias: r1_h ln(1 + r2_h (i - j)) is taken off the scaled score of query i and key j; in the raw
+  // products' units that is (r1_h / (scale log2 e)) log2(1 + r2_h (i - j)). [nq] each, or null.
+  const float* dist_r1;
+  const float* dist_r2;
 };
+// the distance bias of the key `distance` positions behind the query, in the raw products' units
+__device__ __forceinline__ float at_distance(float c_raw, float r2, int distance) {
+  return c_raw * __log2f(fmaf(r2, (float)distance, 1.0f));
+}
 __device__ __forceinline__ float at_cap(float s, float cap_raw, float cap_c2) {
   return cap_raw * (1.f - __fdividef(2.f, 1.f + at_ex2(s * cap_c2)));
 }
@@ -232,9 +240,12 @@ __device__ __forceinline__ void at_rescale(uint32_t t_o, float alpha) {
 // this function and measured slower inside a prompt step (3.60 against 3.53 ms for 2,048 tokens): its
 // 128 live values cost the kernel around the call more than the second read costs here.
 // Returns the sum of the row's exponentials.
+// `keep_off`: offsets below it are seen whatever seen_lo says (the kept first keys of a request). `dist_c`, `dist_r2`,
+// `dist_0`: the distance bias's factor in raw units (0: none), its second number, and the distance of offset 0.
 template <bool CAP>
 __device__ __noinline__ float at_softmax_masked(uint32_t t_s, uint32_t t_o, int seen_lo, int seen_hi, float scale_log2,
-                                                float& m_used, float& l_sum, float cap_raw, float cap_c2) {
+                                                float& m_used, float& l_sum, float cap_raw, float cap_c2, int keep_off,
+                                                float dist_c, float dist_r2, int dist_0) {
   float mx[4] = {-INFINITY, -INFINITY, -INFINITY, -INFINITY};
 #pragma unroll 1
   for (int c = 0; c < 4; ++c) {
@@ -244,8 +255,10 @@ __device__ __noinline__ float at_softmax_masked(uint32_t t_s, uint32_t t_o, int 
 #pragma unroll
     for (int i = 0; i < 32; ++i) {
       const int off = c * 32 + i;
-      const float sc = CAP && cap_c2 > 0.f ? at_cap(v[i], cap_raw, cap_c2) : v[i];
-      mx[i & 3] = fmaxf(mx[i & 3], off <= seen_hi && off >= seen_lo ? sc : -INFINITY);
+      float sc = CAP && cap_c2 > 0.f ? at_cap(v[i], cap_raw, cap_c2) : v[i];
+      const bool seen = off <= seen_hi && (off >= seen_lo || (CAP && off < keep_off));
+      if (CAP && dist_c != 0.f && seen) sc -= at_distance(dist_c, dist_r2, dist_0 - off);
+      mx[i & 3] = fmaxf(mx[i & 3], seen ? sc : -INFINITY);
     }
   }
   const float alpha = at_new_maximum(fmaxf(fmaxf(mx[0], mx[1]), fmaxf(mx[2], mx[3])), m_used, scale_log2);
@@ -268,8 +281,14 @@ __device__ __noinline__ float at_softmax_masked(uint32_t t_s, uint32_t t_o, int 
 #pragma unroll
     for (int i = 0; i < 32; i += 2) {
       const int off = c * 32 + i;
-      const float e0 = off <= seen_hi && off >= seen_lo ? at_ex2(fmaf(v[i], scale_log2, -m_sub)) : 0.f;
-      const float e1 = off + 1 <= seen_hi && off + 1 >= seen_lo ? at_ex2(fmaf(v[i + 1], scale_log2, -m_sub)) : 0.f;
+      const bool seen0 = off <= seen_hi && (off >= seen_lo || (CAP && off < keep_off));
+      const bool seen1 = off + 1 <= seen_hi && (off + 1 >= seen_lo || (CAP && off + 1 < keep_off));
+      if (CAP && dist_c != 0.f) {
+        if (seen0) v[i] -= at_distance(dist_c, dist_r2, dist_0 - off);
+        if (seen1) v[i + 1] -= at_distance(dist_c, dist_r2, dist_0 - off - 1);
+      }
+      const float e0 = seen0 ? at_ex2(fmaf(v[i], scale_log2, -m_sub)) : 0.f;
+      const float e1 = seen1 ? at_ex2(fmaf(v[i + 1], scale_log2, -m_sub)) : 0.f;
       part[(i >> 1) & 3] += e0 + e1;
       __nv_bfloat162 p2 = __floats2bfloat162_rn(e0, e1);
       pk[i >> 1] = *reinterpret_cast<uint32_t*>(&p2);
@@ -286,12 +305,17 @@ struct AtItem {
   int r, rank, tok0, q_len, m0, start, kv_len, head0, split;
   int n_tiles[2], q_first[2], q_last[2], lo_g[2], lo_max[2], shares[2];
   int tile_begin, n_all;
+  // Kept first keys: the walk over key tiles runs over virtual tiles; those below `first_tile` (the window's first
+  // tile) are the request's tiles 0, 1, ... that hold kept keys: virtual tile v is real tile v - walk_shift there.
+  int first_tile, walk_shift;
   bool has_b;
+  __device__ __forceinline__ int real_tile(int v) const { return v < first_tile ? v - walk_shift : v; }
 };
 
 struct AtGrid {
   int q_tiles, rows, head_groups, splits, max_tiles_per_item, window, G;
   int chunk;  // > 0: a query sees only keys from the start of its own block of this many positions on
+  int keep;   // > 0: the first `keep` keys of a request stay visible behind the window (the cache keeps their pages)
   __device__ __forceinline__ int total() const { return q_tiles * rows * head_groups * splits; }
 };
 
@@ -325,7 +349,9 @@ __device__ __forceinline__ bool at_item(AtItem& it, int idx, const AtGrid& gr, c
       it.lo_max[g] = max(it.lo_max[g], (it.q_last[g] / gr.chunk) * gr.chunk);
     }
   }
-  it.tile_begin = it.lo_g[0] / AT_KEYS;
+  it.first_tile = it.lo_g[0] / AT_KEYS;
+  it.walk_shift = it.first_tile - (gr.keep > 0 ? min((gr.keep + AT_KEYS - 1) / AT_KEYS, it.first_tile) : 0);
+  it.tile_begin = it.walk_shift;
   it.n_tiles[0] = (min(it.kv_len, it.q_last[0] + 1) + AT_KEYS - 1) / AT_KEYS - it.tile_begin;
   it.n_tiles[1] = it.has_b ? (min(it.kv_len, it.q_last[1] + 1) + AT_KEYS - 1) / AT_KEYS - it.tile_begin : 0;
   // Key ranges longer than `max_tiles_per_item` are cut into pieces of that length (the last one
@@ -472,7 +498,7 @@ attn_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_c
         bool ok = true;
         for (int j = 0; j < n_all; ++j) {
           const int s = j & 1;
-          const int key0 = (tile_begin + j) * AT_KEYS;
+          const int key0 = it.real_tile(tile_begin + j) * AT_KEYS;
           const int boxes = min(AT_KEYS, ((kv_len - key0 + box_rows - 1) / box_rows) * box_rows) / box_rows;
           int my_row = 0;
           if (lane < boxes) {
@@ -596,6 +622,8 @@ attn_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_c
         const int block_lo = EXTRAS && gr.chunk > 0 ? (qpos / gr.chunk) * gr.chunk : 0;
         // the sink's score in units of log2 (it is neither scaled nor capped)
         const float sink_l2 = EXTRAS && ex.sink_values != nullptr ? ex.sink_values[head0 + hd] * AT_LOG2E : 0.f;
+        const float dist_c = EXTRAS && ex.dist_r1 != nullptr ? ex.dist_r1[head0 + hd] / scale_log2 : 0.f;
+        const float dist_r2 = EXTRAS && ex.dist_r1 != nullptr ? ex.dist_r2[head0 + hd] : 0.f;
         const uint32_t lane_base = (uint32_t)((warp & 3) * 32) << 16;
         const uint32_t t_s = tmem + (uint32_t)(g * 128) + lane_base, t_o = tmem + (uint32_t)(256 + g * 128) + lane_base;
         const int n_mine = it.n_tiles[g];
@@ -604,7 +632,7 @@ attn_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_c
         for (int j = 0; j < n_mine && ok; ++j) {
           if (!at_wait(&s_full[g], j & 1)) { ok = false; break; }
           AT_FENCE_AFTER();
-          const int key0 = (tile_begin + j) * AT_KEYS;
+          const int key0 = it.real_tile(tile_begin + j) * AT_KEYS;
           const bool interior = key0 + AT_KEYS - 1 <= q_first_mine && key0 >= lo_max_mine;
           float part[4] = {0.f, 0.f, 0.f, 0.f};
           if (interior) {
@@ -619,6 +647,13 @@ attn_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_c
               for (int c = 0; c < 4; ++c)
   #pragma unroll
                 for (int i = 0; i < 32; ++i) sv[c][i] = at_cap(sv[c][i], ex.cap_raw, ex.cap_c2);
+            }
+            if (EXTRAS && dist_c != 0.f) {
+              const int d0 = qpos - key0;
+  #pragma unroll
+              for (int c = 0; c < 4; ++c)
+  #pragma unroll
+                for (int i = 0; i < 32; ++i) sv[c][i] -= at_distance(dist_c, dist_r2, d0 - (c * 32 + i));
             }
             float mx[4] = {-INFINITY, -INFINITY, -INFINITY, -INFINITY};
   #pragma unroll
@@ -651,7 +686,8 @@ attn_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_c
             // that this row sees are those at offsets [seen_lo, seen_hi]
             const int seen_hi = qpos - key0;
             const int seen_lo = max(max(lo_mine, block_lo), window > 0 ? qpos - window + 1 : 0) - key0;
-            part[0] = at_softmax_masked<EXTRAS>(t_s, t_o, seen_lo, seen_hi, scale_log2, m_used, l_sum, ex.cap_raw, ex.cap_c2);
+            part[0] = at_softmax_masked<EXTRAS>(t_s, t_o, seen_lo, seen_hi, scale_log2, m_used, l_sum, ex.cap_raw, ex.cap_c2,
+                                                EXTRAS ? gr.keep - key0 : 0, dist_c, dist_r2, qpos - key0);
           }
           l_sum += (part[0] + part[1]) + (part[2] + part[3]);
           const int valid_keys = kv_len - key0;
@@ -896,11 +932,16 @@ MS_EXPORT int ms_attn_tc_prefill(void* out, const void* q, const void* k_pool, c
                                  const int* q_start, const int* page_indptr, const int* page_indices, int num_rows,
                                  int num_tokens, int max_q_len, int nq, int nkv, long long pool_pages, float scale,
                                  int window, int sink, int page_size, int* status, int splits, int min_tiles, float* partials,
-                                 int* queue, const int* plan, cudaStream_t stream, const float* sink_values, float softcap, int chunk) {
+                                 int* queue, const int* plan, cudaStream_t stream, const float* sink_values, float softcap, int chunk,
+                                 const float* dist_r1, const float* dist_r2, int keep_first) {
   MS_CHECK_ARG(softcap >= 0.f && chunk >= 0, "attention_tc: softcap=%g and chunk=%d must not be negative", softcap, chunk);
+  MS_CHECK_ARG(keep_first >= 0 && (keep_first == 0 || window > 0) && (dist_r1 == nullptr) == (dist_r2 == nullptr),
+               "attention_tc: keep_first=%d needs a window, and a distance bias both of its numbers", keep_first);
   sink = sink || sink_values != nullptr;
   AtExtras ex;
   ex.sink_values = sink_values;
+  ex.dist_r1 = dist_r1;
+  ex.dist_r2 = dist_r2;
   ex.cap_raw = softcap > 0.f ? softcap / scale : 0.f;
   ex.cap_c2 = softcap > 0.f ? 2.f * AT_LOG2E * scale / softcap : 0.f;
   // plan: null, or four device ints (tiles of queries per row, rows, key splits, least key tiles per split) that
@@ -962,12 +1003,12 @@ MS_EXPORT int ms_attn_tc_prefill(void* out, const void* q, const void* k_pool, c
     MS_CHECK_CUDA(cudaGetDevice(&dev));
     MS_CHECK_CUDA(cudaDeviceGetAttribute(&sm_count, cudaDevAttrMultiProcessorCount, dev));
   }
-  const AtGrid gr = {ceil_div(max_q_len, 2 * tpc), num_rows, nq / G, splits, min_tiles, window, G, chunk};
+  const AtGrid gr = {ceil_div(max_q_len, 2 * tpc), num_rows, nq / G, splits, min_tiles, window, G, chunk, keep_first};
   const long long total = (long long)gr.q_tiles * gr.rows * gr.head_groups * gr.splits;
   MS_CHECK_ARG(total < (1LL << 30), "attention_tc: %lld work items are too many for one launch", total);
   // one CTA fills an SM (192 KB of shared memory, all of tensor memory) and takes items until none is left
   const unsigned grid = (unsigned)(plan == nullptr && total < sm_count ? total : sm_count);
-  if (sink_values != nullptr || softcap > 0.f || chunk > 0) {
+  if (sink_values != nullptr || softcap > 0.f || chunk > 0 || dist_r1 != nullptr || keep_first > 0) {
     MS_LAUNCH(attn_prefill_tc_kernel<true>, grid, AT_THREADS, smem_bytes, stream, map_q, map_k, map_v, (__nv_bfloat16*)out, cu_q,
               q_start, page_indptr, page_indices, nq, nkv, scale * AT_LOG2E, sink, page_shift, gr, status,
               partials, reinterpret_cast<float2*>(partials + (total / gr.splits) * 2 * gr.splits * (AT_ROWS * AT_D)), queue,

@@ -66,20 +66,25 @@ add_layernorm_kernel(T* __restrict__ out, T* __restrict__ out2, float* __restric
 }
 
 // out[t] = h[t] + (prev - h[t]) * mix, prev = h[t - 1] inside a row's portion; before the portion's first token it is
-// the row's state slot, or zeros when the portion starts the sequence. `out` may not alias `h`.
+// the row's state slot, or zeros when the portion starts the sequence. `out` may not alias `h`. With `update`, the CTA
+// of a portion's first token (the only one that reads the slot) also leaves the portion's last h in the slot: every
+// thread reads the slot's channels it owns before it writes them, so one launch does both.
 template <typename T>
-__global__ void token_shift_kernel(T* __restrict__ out, const T* __restrict__ h, const T* __restrict__ state,
+__global__ void token_shift_kernel(T* __restrict__ out, const T* __restrict__ h, T* __restrict__ state,
                                    const float* __restrict__ mix, const int* __restrict__ row_of_token, const int* __restrict__ cu_q,
-                                   const int* __restrict__ q_start, const int* __restrict__ state_slot, int width) {
+                                   const int* __restrict__ q_start, const int* __restrict__ state_slot, int width, int update) {
   pdl_prologue();
   const int t = blockIdx.x;
   const int row = row_of_token[t];
   const bool first = t == cu_q[row];
-  const T* prev = first ? (q_start[row] > 0 ? state + (size_t)state_slot[row] * width : nullptr) : h + (size_t)(t - 1) * width;
+  T* slot = state + (size_t)state_slot[row] * width;
+  const T* prev = first ? (q_start[row] > 0 ? slot : nullptr) : h + (size_t)(t - 1) * width;
+  const T* newest = h + (size_t)(cu_q[row + 1] - 1) * width;
   for (int c = threadIdx.x; c < width; c += blockDim.x) {
     const float x = Elem<T>::load(h + (size_t)t * width + c);
     const float p = prev ? Elem<T>::load(prev + c) : 0.f;
     Elem<T>::store(out + (size_t)t * width + c, fmaf(p - x, mix[c], x));
+    if (first && update) slot[c] = newest[c];
   }
 }
 
@@ -114,6 +119,33 @@ __global__ void clamped_glu_kernel(T* __restrict__ out, const T* __restrict__ ga
     u = fminf(fmaxf(u, -limit), limit);
   }
   Elem<T>::store(out + idx, g / (1.0f + expf(-alpha * g)) * (u + shift));
+}
+
+// The same for bfloat16 rows whose halves start on 16 bytes: eight channels per thread.
+__global__ void clamped_glu_bf16x8_kernel(__nv_bfloat16* __restrict__ out, const __nv_bfloat16* __restrict__ gate_up,
+                                          const float* __restrict__ bias, int inter8, long long total8, float limit, float alpha,
+                                          float shift) {
+  pdl_prologue();
+  const long long idx = (long long)blockIdx.x * blockDim.x + threadIdx.x;
+  if (idx >= total8) return;
+  const long long t = idx / inter8;
+  const int c = (int)(idx - t * inter8) * 8, inter = inter8 * 8;
+  float g[8], u[8];
+  bf16x8_to_float(*reinterpret_cast<const uint4*>(gate_up + t * 2 * inter + c), g);
+  bf16x8_to_float(*reinterpret_cast<const uint4*>(gate_up + t * 2 * inter + inter + c), u);
+#pragma unroll
+  for (int e = 0; e < 8; ++e) {
+    if (bias) {
+      g[e] += bias[c + e];
+      u[e] += bias[inter + c + e];
+    }
+    if (limit > 0.f) {
+      g[e] = fminf(g[e], limit);
+      u[e] = fminf(fmaxf(u[e], -limit), limit);
+    }
+    g[e] = g[e] / (1.0f + expf(-alpha * g[e])) * (u[e] + shift);
+  }
+  *reinterpret_cast<uint4*>(out + t * inter + c) = float_to_bf16x8(g);
 }
 
 // out = a (+ b) (+ vec on every row): a, b, out [rows, width] in the run's dtype, vec float32 [width]
@@ -694,17 +726,18 @@ MS_EXPORT int ms_add_layernorm(void* out, void* out2, float* residual, const voi
   return 0;
 }
 
-MS_EXPORT int ms_token_shift(void* out, const void* h, const void* state, const float* mix, const int* row_of_token, const int* cu_q,
-                             const int* q_start, const int* state_slot, int tokens, int width, int dtype, cudaStream_t stream) {
+MS_EXPORT int ms_token_shift(void* out, const void* h, void* state, const float* mix, const int* row_of_token, const int* cu_q,
+                             const int* q_start, const int* state_slot, int tokens, int width, int update, int dtype,
+                             cudaStream_t stream) {
   if (tokens == 0) return 0;
   MS_CHECK_ARG(width > 0 && out != h, "token_shift: width=%d, and the output may not be the input", width);
   const int threads = width >= 1024 ? 256 : 128;
   if (dtype == MS_F32)
-    MS_LAUNCH(token_shift_kernel<float>, tokens, threads, 0, stream, (float*)out, (const float*)h, (const float*)state, mix, row_of_token,
-              cu_q, q_start, state_slot, width);
+    MS_LAUNCH(token_shift_kernel<float>, tokens, threads, 0, stream, (float*)out, (const float*)h, (float*)state, mix, row_of_token,
+              cu_q, q_start, state_slot, width, update);
   else
     MS_LAUNCH(token_shift_kernel<__nv_bfloat16>, tokens, threads, 0, stream, (__nv_bfloat16*)out, (const __nv_bfloat16*)h,
-              (const __nv_bfloat16*)state, mix, row_of_token, cu_q, q_start, state_slot, width);
+              (__nv_bfloat16*)state, mix, row_of_token, cu_q, q_start, state_slot, width, update);
   return 0;
 }
 
@@ -725,6 +758,11 @@ MS_EXPORT int ms_clamped_glu(void* out, const void* gate_up, const float* bias, 
   if (tokens == 0 || inter == 0) return 0;
   const long long total = (long long)tokens * inter;
   const unsigned blocks = (unsigned)((total + 255) / 256);
+  if (dtype == MS_BF16 && inter % 8 == 0 && (uintptr_t)out % 16 == 0 && (uintptr_t)gate_up % 16 == 0) {
+    MS_LAUNCH(clamped_glu_bf16x8_kernel, (unsigned)((total / 8 + 255) / 256), 256, 0, stream, (__nv_bfloat16*)out,
+              (const __nv_bfloat16*)gate_up, bias, inter / 8, total / 8, limit, alpha, shift);
+    return 0;
+  }
   if (dtype == MS_F32)
     MS_LAUNCH(clamped_glu_kernel<float>, blocks, 256, 0, stream, (float*)out, (const float*)gate_up, bias, inter, total, limit, alpha, shift);
   else

@@ -547,8 +547,7 @@ def attention(out: torch.Tensor, q: torch.Tensor, k_pool: torch.Tensor, v_pool: 
         return
     recorder = getattr(ctx, "recorder", None)
     split_ok = q.dtype == torch.bfloat16 and attention_bf16.supports(q.shape[2], k_pool.shape[2])
-    # (a distance bias and kept first keys are in the mma.sync kernels and the row-wise kernel, not in the tcgen05 kernel)
-    tc_ok = q.dtype == torch.bfloat16 and not (extras is not None and extras.positional) and attention_tc_ok(q, k_pool)
+    tc_ok = q.dtype == torch.bfloat16 and attention_tc_ok(q, k_pool)
     if recorder is not None and (tc_ok or split_ok):
         # The pass is being captured into CUDA graphs. Which tensor-core kernels run here, their grids and
         # their key splits depend on each row's length and start, which a graph cannot hold.
@@ -607,8 +606,9 @@ _ATTN_TC_PLANNED_SCRATCH = 1 << 25  # floats of partial results that a captured 
 
 def _extras_args(extras) -> tuple:
     if extras is None:
-        return (None, 0.0, 0)
-    return (_ptr(extras.sink_values), float(extras.softcap or 0.0), int(extras.chunk or 0))
+        return (None, 0.0, 0, None, None, 0)
+    return (_ptr(extras.sink_values), float(extras.softcap or 0.0), int(extras.chunk or 0), _ptr(extras.dist_r1), _ptr(extras.dist_r2),
+            int(extras.keep_first or 0))
 
 
 def _attention_tc_planned(out, q, k_pool, v_pool, ctx, group: int, scale: float, window: int | None, recorder,

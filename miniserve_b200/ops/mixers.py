@@ -137,16 +137,17 @@ def add_layernorm(out, residual, delta, weight, bias, eps: float, rows=None, num
         _ptr(rows), float(eps), n, hidden, int(write_residual and rows is None), _dt(out.dtype), _stream(stream)))
 
 
-def token_shift(out, h, state, mix, ctx) -> None:
+def token_shift(out, h, state, mix, ctx, update: bool = True) -> None:
     """out[t] = h[t] + (h[t - 1] - h[t]) * mix (float32 [width]); the token before a row's first one in this step is the
-    row's slot of ``state`` [slots, width], or zeros where the row starts its sequence. ``out`` is not ``h``."""
+    row's slot of ``state`` [slots, width], or zeros where the row starts its sequence. ``out`` is not ``h``. With
+    ``update`` the same launch leaves each row's last h of this step in its slot."""
     t, width = h.shape
     _f32(mix)
     assert out.shape == h.shape and out.dtype == h.dtype == state.dtype and out.is_contiguous() and h.is_contiguous()
     assert state.is_contiguous() and state.shape[1] == width and mix.numel() == width and out.data_ptr() != h.data_ptr()
     native.mixers_check(native.mixers().ms_token_shift(
         _ptr(out), _ptr(h), _ptr(state), _ptr(mix), _ptr(ctx.row_of_token), _ptr(ctx.cu_q), _ptr(ctx.q_start), _ptr(ctx.state_slot),
-        t, width, _dt(h.dtype), ctx.stream))
+        t, width, int(update), _dt(h.dtype), ctx.stream))
 
 
 def shift_state_update(state, h, ctx) -> None:

@@ -141,7 +141,7 @@ def mixers():
     _declare(lib, "ms_latent_rope_prepare", [_p, _p, _i, _p, _f, _p, _i, _i, _i, _p, _p, _p, _p, _p, _p, _i, _i, _i, _i, _i, _i, _p, _i, _p])
     _declare(lib, "ms_act_mul", [_p, _p, _i, _i, _i, _i, _p])
     _declare(lib, "ms_add_layernorm", [_p, _p, _p, _p, _f, _p, _p, _p, _p, _p, _f, _i, _i, _i, _i, _p])
-    _declare(lib, "ms_token_shift", [_p, _p, _p, _p, _p, _p, _p, _p, _i, _i, _i, _p])
+    _declare(lib, "ms_token_shift", [_p, _p, _p, _p, _p, _p, _p, _p, _i, _i, _i, _i, _p])
     _declare(lib, "ms_shift_state_update", [_p, _p, _p, _p, _i, _i, _i, _p])
     _declare(lib, "ms_clamped_glu", [_p, _p, _p, _i, _i, _f, _f, _f, _i, _p])
     _declare(lib, "ms_sum_bias", [_p, _p, _p, _p, _i, _i, _i, _p])
@@ -219,7 +219,7 @@ def attn_tc():
     _declare(lib, "ms_attn_tc_supports", [_i, _i, _i, _i])
     _declare(lib, "ms_attn_tc_plan", [_p, _p, _i, _i, _i, _i, _i, _p, _p], None)
     _declare(lib, "ms_attn_tc_scratch", [_i, _i, _i, _i, _i, _p, _p], None)
-    _declare(lib, "ms_attn_tc_prefill", [_p] * 8 + [_i, _i, _i, _i, _i, _ll, _f, _i, _i, _i, _p, _i, _i, _p, _p, _p, _p, _p, _f, _i])
+    _declare(lib, "ms_attn_tc_prefill", [_p] * 8 + [_i, _i, _i, _i, _i, _ll, _f, _i, _i, _i, _p, _i, _i, _p, _p, _p, _p, _p, _f, _i, _p, _p, _i])
     _declare(lib, "ms_attn_tc_write_plan", [_p, _p, _p, _i, _i, _i, _i, _i, _i, _ll, _ll, _p])
     lib.ms_attn_tc_set_pdl(int(pdl_enabled()))
     return lib

@@ -194,7 +194,7 @@ class GQAttention(Part):
         return self._own_reach() or None
 
     def features(self, x: torch.Tensor, ctx, cache, out: torch.Tensor | None, scale: float = 1.0, proj: torch.Tensor | None = None,
-                 defer_gate: bool = False):
+                 defer_gate: bool = False, raw: bool = False):
         """The general path up to the output projection's input: ``out`` [T, heads * value_dim] (a view
         whose rows may be part of wider ones) = scale * gate * attention. ``proj``: the q|k|v|gate projection if
         the caller made it already (columns of a wider product, in this mixer's order). ``defer_gate`` (per-channel
@@ -217,6 +217,8 @@ class GQAttention(Part):
                         cache.page_size, ctx.status, stream=ctx.stream, bias=self.w_bias, unit_norm=self.unit_norm, q_scale=self.w_temp)
         att = ctx.buffer("attn.out", (t, nq, dc), dt, dev)
         ops.attention(att, q, cache.k, cache.v, ctx, cache.group, self.scale, self.reach, self.sink, extras=self.extras)
+        if raw:  # the caller takes attention's output [T, heads, D] itself (no gate, values as wide as the cache's heads)
+            return att
         if self.out_gate == "channel_sigmoid":
             if defer_gate:
                 return att, proj[:, at_g:at_g + nq * dv]
@@ -230,8 +232,12 @@ class GQAttention(Part):
         t = x.shape[0]
         dt, dev = self.env.dtype, x.device
         if self.general:
-            feat = ctx.buffer("attn.feat", (t, self.feature_width), dt, dev)
-            self.features(x, ctx, cache, feat)
+            if not self.out_gate and self.value_dim == self.cache_dim:
+                # nothing to cut and nothing to gate: attention's output is the output product's input as it stands
+                feat = self.features(x, ctx, cache, None, raw=True).view(t, self.feature_width)
+            else:
+                feat = ctx.buffer("attn.feat", (t, self.feature_width), dt, dev)
+                self.features(x, ctx, cache, feat)
             return ops.linear(feat, self.w_o, stream=ctx.stream, out=ctx.buffer("attn.proj", (t, self.w_o.shape[0]), dt, dev))
         q = ctx.buffer("attn.q", (t, self.heads, self.head_dim), dt, dev)
         inv_freq, rotary_dim = self.position.kernel_table()

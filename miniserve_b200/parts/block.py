@@ -165,8 +165,7 @@ class TokenShift(Part):
 
     def forward(self, h: torch.Tensor, ctx, cache) -> torch.Tensor:
         out = ctx.buffer("shift.out", tuple(h.shape), h.dtype, h.device)
-        ops.token_shift(out, h, cache.state, self.w_mix, ctx)
-        ops.shift_state_update(cache.state, h, ctx)  # after the read: the first token of a portion and its last may be far apart
+        ops.token_shift(out, h, cache.state, self.w_mix, ctx)  # (and the portion's last h into the slot, by the CTA that read it)
         return out
 
 
@@ -223,9 +222,11 @@ class ParallelDualNormBlock(Part):
         a = self.mixer.forward(h1, ctx, cache)
         if not self.has_ff:
             return ResidualStream(total, a)
-        b = self.feed_forward.forward(h2, ctx)
+        # a bias on the feed-forward's output is added in the same kernel as the two sublayers' outputs
+        bias = getattr(self.feed_forward, "output_bias", None)
+        b = self.feed_forward.forward(h2, ctx, with_bias=False) if bias is not None else self.feed_forward.forward(h2, ctx)
         y = ctx.buffer("block.out", tuple(a.shape), self.env.dtype, a.device)
-        ops.axpby(y, a, b, 1.0, 1.0, stream=ctx.stream)
+        ops.sum_bias(y, a, b, bias, stream=ctx.stream)
         return ResidualStream(total, y)
 
 

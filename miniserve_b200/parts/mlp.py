@@ -110,13 +110,19 @@ class ClampedGLU(Part):
         self.w_in_bias = torch.cat([tensors[n["gate_bias"]].float(), tensors[n["up_bias"]].float()]).contiguous() if self.bias else None
         self.w_out_bias = tensors[n["down_bias"]].float().contiguous() if self.bias else None
 
-    def forward(self, x, ctx) -> torch.Tensor:
+    @property
+    def output_bias(self) -> torch.Tensor | None:
+        """The down projection's bias (float32), for a caller that adds it together with something else
+        (``forward(..., with_bias=False)``)."""
+        return self.w_out_bias
+
+    def forward(self, x, ctx, with_bias: bool = True) -> torch.Tensor:
         t, dt, dev = x.shape[0], self.env.dtype, self.w_down.device
         gate_up = ops.linear(x, self.w_gate_up, stream=ctx.stream, out=ctx.buffer("mlp.gate_up", (t, 2 * self.inter), dt, dev))
         act = ctx.buffer("mlp.act", (t, self.inter), dt, dev)
         ops.clamped_glu(act, gate_up, self.w_in_bias, self.limit, self.alpha, self.up_shift, stream=ctx.stream)
         out = ops.linear(act, self.w_down, stream=ctx.stream, out=ctx.buffer("mlp.down", (t, self.hidden), dt, dev))
-        if self.w_out_bias is not None:
+        if with_bias and self.w_out_bias is not None:
             ops.sum_bias(out, out, None, self.w_out_bias, stream=ctx.stream)
         return out
 

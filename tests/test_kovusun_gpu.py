@@ -244,16 +244,20 @@ def _needle_for(att):
 
 
 @pytest.mark.parametrize("dtype", DTYPES)
-@pytest.mark.parametrize("kind, window, keep, n, page", [
+@pytest.mark.parametrize("kind, window, keep, n, page, dim", [case if len(case) == 6 else case + (32,) for case in [
     ("attention", 16, 0, 41, 8), ("attention", 20, 0, 75, 16), ("attention_2", 5, 0, 30, 8), ("attention_2", 64, 0, 200, 16),
     ("attention_2", 1, 0, 9, 4), ("attention", 512, 0, 700, 16), ("attention_3", 16, 4, 60, 8), ("attention_3", 20, 17, 90, 16),
-    ("attention_3", 33, 1, 300, 16), ("attention_3", 1024, 3, 1900, 16), ("attention_3", 7, 0, 40, 8)])
-def test_a_key_just_inside_and_just_outside_the_window_and_the_kept_keys(dtype, kind, window, keep, n, page):
+    ("attention_3", 33, 1, 300, 16), ("attention_3", 1024, 3, 1900, 16), ("attention_3", 7, 0, 40, 8),
+    # heads of 128: bfloat16 prompts run on the tcgen05 kernel (kept keys in a tile of their own, in the window's first
+    # tile, and none), decoded tokens on the split-key kernel
+    ("attention_3", 200, 5, 700, 16, 128), ("attention_3", 100, 130, 600, 16, 128), ("attention_3", 300, 2, 350, 32, 128),
+    ("attention", 300, 0, 700, 16, 128), ("attention_2", 129, 0, 400, 16, 128)]])
+def test_a_key_just_inside_and_just_outside_the_window_and_the_kept_keys(dtype, kind, window, keep, n, page, dim):
     """The last query and one earlier token are made so that this pair scores far above everything else. With the
     earlier token window - 1 places back its value must come back; one place further it must not, unless it is one of
     the kept first keys (the last kept one shows, the one behind it does not): in a prompt, for a token decoded alone
     and in a short portion. A window of one sees only the token itself."""
-    sizes = dict(heads=4, kv_heads=2, dim=32, vdim=32, window=window, scale=0.5)
+    sizes = dict(heads=4, kv_heads=2, dim=dim, vdim=dim, window=window, scale=0.5 if dim == 32 else 0.05)
     if kind == "attention_3":
         sizes.update(keep_first=keep, rot=4, base=10000.0)  # (a slow rotation of few channels: the needle survives the distance)
     att, m = _mixer(dtype, kind, **sizes)
@@ -282,28 +286,33 @@ def test_a_key_just_inside_and_just_outside_the_window_and_the_kept_keys(dtype, 
 
 
 @pytest.mark.parametrize("dtype", DTYPES)
-def test_distance_bias_prefers_near_keys_by_head(dtype):
+@pytest.mark.parametrize("dim, n, window", [(16, 37, 40), (128, 300, 400), (128, 420, 150)])
+def test_distance_bias_prefers_near_keys_by_head(dtype, dim, n, window):
     """All keys equal: the scores differ by the distance bias alone. A head with r1 > 0 weighs near keys more, one with
     r1 < 0 far keys, one with r1 = 0 all alike; the engine agrees with the plain form in a prompt and in decoding."""
-    att, m = _mixer(dtype, "attention", heads=3, kv_heads=1, dim=16, vdim=16, window=40, scale=0.3)
+    att, m = _mixer(dtype, "attention", heads=3, kv_heads=1, dim=dim, vdim=16, window=window, scale=0.3)
 
     def change(t):
         t["r1"].copy_(torch.tensor([6.0, -6.0, 0.0]))
         t["r2"].copy_(torch.tensor([0.5, 2.0, 1.0]))
         t["k"].zero_()  # the keys are their biases: the same at every position
     w = _bind(att, dtype, change=change)
-    n = 37
     x = _x(n, dtype, 1.0)
     ref = _ref(x, w, m, "attention")
-    full, ctx = _ctx([(0, n)], 8, 1, att.cache_dim, dtype, seed=4)
-    view = KVEntryView(0, full.k_pool, full.v_pool, 8)
+    full, ctx = _ctx([(0, n)], 16, 1, att.cache_dim, dtype, seed=4)
+    view = KVEntryView(0, full.k_pool, full.v_pool, 16)
     _close(att.forward(x, ctx, view), ref, dtype, 3.0)
-    _, ctx = _ctx([(n - 1, 1)], 8, 1, att.cache_dim, dtype, share=full)
+    _, ctx = _ctx([(n - 1, 1)], 16, 1, att.cache_dim, dtype, share=full)
     _close(att.forward(x[n - 1:].contiguous(), ctx, view), ref[n - 1:], dtype, 3.0)
+    _, ctx = _ctx([(n - 70, 70)], 16, 1, att.cache_dim, dtype, share=full)
+    _close(att.forward(x[n - 70:].contiguous(), ctx, view), ref[n - 70:], dtype, 3.0) if n > 70 else None
+    first = max(0, n - window)  # the last query's first visible key
     v = (_cpu(x).double() @ w["v"].double().T + w["v.b"].double()).float()  # [n, 16]
     o = (ref[n - 1].double() @ torch.linalg.pinv(w["o"].double()).T).float().view(3, 16)
-    assert (o[2] - v.mean(0)).abs().max() < 1e-3, "without a bias every key weighs the same"
-    assert (o[0] - v[n - 1]).norm() < 0.5 * (o[0] - v[0]).norm() and (o[1] - v[:10].mean(0)).norm() < 0.5 * (o[1] - v[n - 10:].mean(0)).norm()
+    assert (o[2] - v[first:].mean(0)).abs().max() < 1e-3, "without a bias every key weighs the same"
+    assert (o[0] - v[n - 1]).norm() < 0.5 * (o[0] - v[first]).norm()
+    third = (n - first) // 3
+    assert (o[1] - v[first:first + third].mean(0)).norm() < (o[1] - v[n - third:].mean(0)).norm()
 
 
 @pytest.mark.parametrize("dtype", DTYPES)
