@@ -45,7 +45,27 @@ def _mugipel(width, vocab, ff, pattern, attention, latent, loop, mult) -> dict:
     return raw
 
 
+def _kovusun(width, vocab, ff, heads, kv_heads, dim, window) -> dict:
+    """A Kovusun config.json of four layers: attention with a distance bias, rotary attention with kept first keys,
+    attention that reads the first layer's keys and values, attention with a sink and a gate; dense and routed
+    feed-forwards in turn."""
+    base = {"dim": dim, "heads": heads, "kv_heads": kv_heads, "mask": {"size": window}, "scale": dim ** -0.5, "vdim": dim}
+    dense = {"ff": ff, "kind": "dense", "limit": 4.0}
+    moe = {"kind": "moe", "expert": {"ff": ff // 4}, "router": {"experts": 6, "top": 2}, "shared": {"ff": ff // 2}}
+    layers = []
+    for i, kind in enumerate(("attention", "attention_3", "attention", "attention_2")):
+        mixer = {k: (dict(v) if isinstance(v, dict) else v) for k, v in base.items()}
+        if kind == "attention_3":
+            mixer["mask"]["keep_first"] = 2
+            mixer["rot"] = {"base": 10000.0, "dims": dim // 2}
+        if i == 2:
+            mixer["kv_from"] = 0
+        layers.append({"type": kind, "mixer": mixer, "mlp": dict(moe if i % 2 else dense)})
+    return dict(architecture="Kovusun", width=width, vocab=vocab, norm={"eps": 1e-5}, layers=layers)
+
+
 PRESETS: dict[str, dict] = {
+    "kovusun-tiny": _kovusun(96, 503, 160, 6, 2, 32, 48),
     "mugipel-tiny": _mugipel(
         96, 503, 160, "ALAL",
         attention={"dim": 32, "heads": 6, "kv_heads": 2, "mask": {"size": 64}, "scale": 32 ** -0.5, "softcap": 30.0, "vdim": 32,

@@ -14,7 +14,7 @@ from pathlib import Path
 
 def main(argv=None) -> int:
     ap = argparse.ArgumentParser(description=__doc__.splitlines()[0])
-    ap.add_argument("--preset", default=None, help="tiny-a, tiny-b, 0.6b, 1.7b, 8b, 32b, fekulix-tiny or mugipel-tiny")
+    ap.add_argument("--preset", default=None, help="tiny-a, tiny-b, 0.6b, 1.7b, 8b, 32b, fekulix-tiny, mugipel-tiny or kovusun-tiny")
     ap.add_argument("--config", default=None, help="a config.json to take the sizes from")
     ap.add_argument("--seed", type=int, default=0)
     ap.add_argument("--out", required=True)
