@@ -65,6 +65,66 @@ add_layernorm_kernel(T* __restrict__ out, T* __restrict__ out2, float* __restric
   }
 }
 
+// bfloat16 rows that are a multiple of 8 wide and at most 8 * THREADS: eight elements per thread, kept in registers
+template <int THREADS>
+__global__ void __launch_bounds__(THREADS)
+add_layernorm_bf16x8_kernel(__nv_bfloat16* __restrict__ out, __nv_bfloat16* __restrict__ out2, float* __restrict__ residual,
+                            const __nv_bfloat16* __restrict__ delta, float delta_scale, const float* __restrict__ w,
+                            const float* __restrict__ b, const float* __restrict__ w2, const float* __restrict__ b2,
+                            const int* __restrict__ rows, float eps, int hidden, int write_residual) {
+  __shared__ float red[32];
+  pdl_prologue();
+  const int i = blockIdx.x;
+  const int r = rows ? rows[i] : i;
+  float* res = residual + (size_t)r * hidden;
+  const __nv_bfloat16* dl = delta ? delta + (size_t)r * hidden : nullptr;
+  const int c = threadIdx.x;
+  const bool mine = c < (hidden >> 3);
+  float h[8] = {0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f};
+  float sum = 0.f;
+  if (mine) {
+    const float4 a = *reinterpret_cast<const float4*>(res + 8 * c), b4 = *reinterpret_cast<const float4*>(res + 8 * c + 4);
+    h[0] = a.x; h[1] = a.y; h[2] = a.z; h[3] = a.w; h[4] = b4.x; h[5] = b4.y; h[6] = b4.z; h[7] = b4.w;
+    if (dl) {
+      float d[8];
+      bf16x8_to_float(*reinterpret_cast<const uint4*>(dl + 8 * c), d);
+#pragma unroll
+      for (int e = 0; e < 8; ++e) h[e] = fmaf(delta_scale, d[e], h[e]);
+    }
+#pragma unroll
+    for (int e = 0; e < 8; ++e) sum += h[e];
+  }
+  const float mean = block_sum(sum, red) / (float)hidden;
+  float dev = 0.f;
+  if (mine) {
+#pragma unroll
+    for (int e = 0; e < 8; ++e) dev += (h[e] - mean) * (h[e] - mean);
+  }
+  const float inv = 1.0f / sqrtf(block_sum(dev, red) / (float)hidden + eps);
+  if (!mine) return;
+  if (write_residual && dl) {
+    *reinterpret_cast<float4*>(res + 8 * c) = make_float4(h[0], h[1], h[2], h[3]);
+    *reinterpret_cast<float4*>(res + 8 * c + 4) = make_float4(h[4], h[5], h[6], h[7]);
+  }
+  float y[8];
+  {
+    const float4 wa = *reinterpret_cast<const float4*>(w + 8 * c), wb = *reinterpret_cast<const float4*>(w + 8 * c + 4);
+    const float4 ba = *reinterpret_cast<const float4*>(b + 8 * c), bb = *reinterpret_cast<const float4*>(b + 8 * c + 4);
+    const float wv[8] = {wa.x, wa.y, wa.z, wa.w, wb.x, wb.y, wb.z, wb.w}, bv[8] = {ba.x, ba.y, ba.z, ba.w, bb.x, bb.y, bb.z, bb.w};
+#pragma unroll
+    for (int e = 0; e < 8; ++e) y[e] = (h[e] - mean) * inv * wv[e] + bv[e];
+    *reinterpret_cast<uint4*>(out + (size_t)i * hidden + 8 * c) = float_to_bf16x8(y);
+  }
+  if (out2) {
+    const float4 wa = *reinterpret_cast<const float4*>(w2 + 8 * c), wb = *reinterpret_cast<const float4*>(w2 + 8 * c + 4);
+    const float4 ba = *reinterpret_cast<const float4*>(b2 + 8 * c), bb = *reinterpret_cast<const float4*>(b2 + 8 * c + 4);
+    const float wv[8] = {wa.x, wa.y, wa.z, wa.w, wb.x, wb.y, wb.z, wb.w}, bv[8] = {ba.x, ba.y, ba.z, ba.w, bb.x, bb.y, bb.z, bb.w};
+#pragma unroll
+    for (int e = 0; e < 8; ++e) y[e] = (h[e] - mean) * inv * wv[e] + bv[e];
+    *reinterpret_cast<uint4*>(out2 + (size_t)i * hidden + 8 * c) = float_to_bf16x8(y);
+  }
+}
+
 // out[t] = h[t] + (prev - h[t]) * mix, prev = h[t - 1] inside a row's portion; before the portion's first token it is
 // the row's state slot, or zeros when the portion starts the sequence. `out` may not alias `h`. With `update`, the CTA
 // of a portion's first token (the only one that reads the slot) also leaves the portion's last h in the slot: every
@@ -85,6 +145,31 @@ __global__ void token_shift_kernel(T* __restrict__ out, const T* __restrict__ h,
     const float p = prev ? Elem<T>::load(prev + c) : 0.f;
     Elem<T>::store(out + (size_t)t * width + c, fmaf(p - x, mix[c], x));
     if (first && update) slot[c] = newest[c];
+  }
+}
+
+// The same for bfloat16 rows that are a multiple of 8 wide and start on 16 bytes: eight channels per thread.
+__global__ void token_shift_bf16x8_kernel(__nv_bfloat16* __restrict__ out, const __nv_bfloat16* __restrict__ h,
+                                          __nv_bfloat16* __restrict__ state, const float* __restrict__ mix,
+                                          const int* __restrict__ row_of_token, const int* __restrict__ cu_q,
+                                          const int* __restrict__ q_start, const int* __restrict__ state_slot, int width, int update) {
+  pdl_prologue();
+  const int t = blockIdx.x;
+  const int row = row_of_token[t];
+  const bool first = t == cu_q[row];
+  __nv_bfloat16* slot = state + (size_t)state_slot[row] * width;
+  const __nv_bfloat16* prev = first ? (q_start[row] > 0 ? slot : nullptr) : h + (size_t)(t - 1) * width;
+  const __nv_bfloat16* newest = h + (size_t)(cu_q[row + 1] - 1) * width;
+  for (int c = threadIdx.x * 8; c < width; c += blockDim.x * 8) {
+    float x[8], p[8] = {0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f};
+    bf16x8_to_float(*reinterpret_cast<const uint4*>(h + (size_t)t * width + c), x);
+    if (prev) bf16x8_to_float(*reinterpret_cast<const uint4*>(prev + c), p);
+    const float4 ma = *reinterpret_cast<const float4*>(mix + c), mb = *reinterpret_cast<const float4*>(mix + c + 4);
+    const float m[8] = {ma.x, ma.y, ma.z, ma.w, mb.x, mb.y, mb.z, mb.w};
+#pragma unroll
+    for (int e = 0; e < 8; ++e) x[e] = fmaf(p[e] - x[e], m[e], x[e]);
+    *reinterpret_cast<uint4*>(out + (size_t)t * width + c) = float_to_bf16x8(x);
+    if (first && update) *reinterpret_cast<uint4*>(slot + c) = *reinterpret_cast<const uint4*>(newest + c);
   }
 }
 
@@ -133,17 +218,20 @@ __global__ void clamped_glu_bf16x8_kernel(__nv_bfloat16* __restrict__ out, const
   float g[8], u[8];
   bf16x8_to_float(*reinterpret_cast<const uint4*>(gate_up + t * 2 * inter + c), g);
   bf16x8_to_float(*reinterpret_cast<const uint4*>(gate_up + t * 2 * inter + inter + c), u);
+  if (bias) {  // (rows of whole 16 bytes: c and inter are multiples of 8)
+    const float4 ga = *reinterpret_cast<const float4*>(bias + c), gb = *reinterpret_cast<const float4*>(bias + c + 4);
+    const float4 ua = *reinterpret_cast<const float4*>(bias + inter + c), ub = *reinterpret_cast<const float4*>(bias + inter + c + 4);
+    g[0] += ga.x; g[1] += ga.y; g[2] += ga.z; g[3] += ga.w; g[4] += gb.x; g[5] += gb.y; g[6] += gb.z; g[7] += gb.w;
+    u[0] += ua.x; u[1] += ua.y; u[2] += ua.z; u[3] += ua.w; u[4] += ub.x; u[5] += ub.y; u[6] += ub.z; u[7] += ub.w;
+  }
 #pragma unroll
   for (int e = 0; e < 8; ++e) {
-    if (bias) {
-      g[e] += bias[c + e];
-      u[e] += bias[inter + c + e];
-    }
     if (limit > 0.f) {
       g[e] = fminf(g[e], limit);
       u[e] = fminf(fmaxf(u[e], -limit), limit);
     }
-    g[e] = g[e] / (1.0f + expf(-alpha * g[e])) * (u[e] + shift);
+    // (fast exponential and division: relative error about 1e-6, far below the bfloat16 rounding of the result)
+    g[e] = __fdividef(g[e], 1.0f + __expf(-alpha * g[e])) * (u[e] + shift);
   }
   *reinterpret_cast<uint4*>(out + t * inter + c) = float_to_bf16x8(g);
 }
@@ -705,11 +793,47 @@ MS_EXPORT int ms_latent_rope_prepare(void* pool, const void* kv, int ld_kv, cons
   return 0;
 }
 
+namespace ms {
+__global__ void sum_bias_bf16x8_kernel(__nv_bfloat16* __restrict__ out, const __nv_bfloat16* __restrict__ a,
+                                       const __nv_bfloat16* __restrict__ b, const float* __restrict__ vec, long long total8, int width) {
+  pdl_prologue();
+  const long long i = (long long)blockIdx.x * blockDim.x + threadIdx.x;
+  if (i >= total8) return;
+  float x[8], y[8];
+  bf16x8_to_float(*reinterpret_cast<const uint4*>(a + 8 * i), x);
+  if (b) {
+    bf16x8_to_float(*reinterpret_cast<const uint4*>(b + 8 * i), y);
+#pragma unroll
+    for (int e = 0; e < 8; ++e) x[e] += y[e];
+  }
+  if (vec) {
+    const int c = (int)((8 * i) % width);
+    const float4 va = *reinterpret_cast<const float4*>(vec + c), vb = *reinterpret_cast<const float4*>(vec + c + 4);
+    x[0] += va.x; x[1] += va.y; x[2] += va.z; x[3] += va.w; x[4] += vb.x; x[5] += vb.y; x[6] += vb.z; x[7] += vb.w;
+  }
+  *reinterpret_cast<uint4*>(out + 8 * i) = float_to_bf16x8(x);
+}
+}  // namespace ms
+
 MS_EXPORT int ms_add_layernorm(void* out, void* out2, float* residual, const void* delta, float delta_scale, const float* w,
                                const float* b, const float* w2, const float* b2, const int* rows, float eps, int n, int hidden,
                                int write_residual, int dtype, cudaStream_t stream) {
   if (n == 0) return 0;
   MS_CHECK_ARG(hidden > 0 && w && b && (out2 == nullptr || (w2 && b2)), "add_layernorm: hidden=%d, or a norm without weight and bias", hidden);
+  if (dtype == MS_BF16 && hidden % 8 == 0 && hidden <= 8 * 1024 && (uintptr_t)out % 16 == 0 && (uintptr_t)out2 % 16 == 0 &&
+      (uintptr_t)residual % 16 == 0 && (uintptr_t)delta % 16 == 0 && (uintptr_t)w % 16 == 0 && (uintptr_t)b % 16 == 0 &&
+      (uintptr_t)w2 % 16 == 0 && (uintptr_t)b2 % 16 == 0) {
+    const int chunks = hidden / 8;
+#define MS_LN_LAUNCH(THREADS)                                                                                                   \
+  MS_LAUNCH(add_layernorm_bf16x8_kernel<THREADS>, n, THREADS, 0, stream, (__nv_bfloat16*)out, (__nv_bfloat16*)out2, residual,     \
+            (const __nv_bfloat16*)delta, delta_scale, w, b, w2, b2, rows, eps, hidden, write_residual)
+    if (chunks <= 128) MS_LN_LAUNCH(128);
+    else if (chunks <= 256) MS_LN_LAUNCH(256);
+    else if (chunks <= 512) MS_LN_LAUNCH(512);
+    else MS_LN_LAUNCH(1024);
+#undef MS_LN_LAUNCH
+    return 0;
+  }
   const size_t smem = (size_t)hidden * sizeof(float);
   MS_CHECK_ARG(smem <= 200 * 1024, "add_layernorm: a row of %d floats does not fit shared memory", hidden);
   if (dtype == MS_F32) {
@@ -732,6 +856,12 @@ MS_EXPORT int ms_token_shift(void* out, const void* h, void* state, const float*
   if (tokens == 0) return 0;
   MS_CHECK_ARG(width > 0 && out != h, "token_shift: width=%d, and the output may not be the input", width);
   const int threads = width >= 1024 ? 256 : 128;
+  if (dtype == MS_BF16 && width % 8 == 0 && (uintptr_t)out % 16 == 0 && (uintptr_t)h % 16 == 0 && (uintptr_t)state % 16 == 0 &&
+      (uintptr_t)mix % 16 == 0) {
+    MS_LAUNCH(token_shift_bf16x8_kernel, tokens, width >= 2048 ? 256 : 128, 0, stream, (__nv_bfloat16*)out, (const __nv_bfloat16*)h,
+              (__nv_bfloat16*)state, mix, row_of_token, cu_q, q_start, state_slot, width, update);
+    return 0;
+  }
   if (dtype == MS_F32)
     MS_LAUNCH(token_shift_kernel<float>, tokens, threads, 0, stream, (float*)out, (const float*)h, (float*)state, mix, row_of_token,
               cu_q, q_start, state_slot, width, update);
@@ -758,7 +888,7 @@ MS_EXPORT int ms_clamped_glu(void* out, const void* gate_up, const float* bias, 
   if (tokens == 0 || inter == 0) return 0;
   const long long total = (long long)tokens * inter;
   const unsigned blocks = (unsigned)((total + 255) / 256);
-  if (dtype == MS_BF16 && inter % 8 == 0 && (uintptr_t)out % 16 == 0 && (uintptr_t)gate_up % 16 == 0) {
+  if (dtype == MS_BF16 && inter % 8 == 0 && (uintptr_t)out % 16 == 0 && (uintptr_t)gate_up % 16 == 0 && (uintptr_t)bias % 16 == 0) {
     MS_LAUNCH(clamped_glu_bf16x8_kernel, (unsigned)((total / 8 + 255) / 256), 256, 0, stream, (__nv_bfloat16*)out,
               (const __nv_bfloat16*)gate_up, bias, inter / 8, total / 8, limit, alpha, shift);
     return 0;
@@ -775,6 +905,12 @@ MS_EXPORT int ms_sum_bias(void* out, const void* a, const void* b, const float* 
   if (rows == 0 || width == 0) return 0;
   const long long total = (long long)rows * width;
   const unsigned blocks = (unsigned)((total + 255) / 256);
+  if (dtype == MS_BF16 && width % 8 == 0 && (uintptr_t)out % 16 == 0 && (uintptr_t)a % 16 == 0 && (uintptr_t)b % 16 == 0 &&
+      (uintptr_t)vec % 16 == 0) {
+    MS_LAUNCH(sum_bias_bf16x8_kernel, (unsigned)((total / 8 + 255) / 256), 256, 0, stream, (__nv_bfloat16*)out, (const __nv_bfloat16*)a,
+              (const __nv_bfloat16*)b, vec, total / 8, width);
+    return 0;
+  }
   if (dtype == MS_F32)
     MS_LAUNCH(sum_bias_kernel<float>, blocks, 256, 0, stream, (float*)out, (const float*)a, (const float*)b, vec, total, width);
   else

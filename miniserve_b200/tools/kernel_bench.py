@@ -114,7 +114,11 @@ def main(argv=None) -> int:
     ap.add_argument("--chunk", type=int, default=0, help="attn_*: a query sees only its own block of this many positions (0: all)")
     ap.add_argument("--learned-sink", action="store_true", help="attn_*: a sink with a score per head")
     ap.add_argument("--offset", action="store_true", help="add_rmsnorm: the kernel with a float32 weight stored around zero and a factor on the addend")
-    ap.add_argument("--op", choices=["channel_gate", "head_gate", "relu_squared", "gelu_tanh", "latent_prepare", "qkv_prepare"],
+    ap.add_argument("--distance-bias", action="store_true", help="attn_*: r1 ln(1 + r2 distance) taken off the scores, numbers per head")
+    ap.add_argument("--keep-first", type=int, default=0, help="attn_*: this many first keys stay visible behind --window")
+    ap.add_argument("--window", type=int, default=0, help="attn_*: a query sees only this many keys back (0: all)")
+    ap.add_argument("--op", choices=["channel_gate", "head_gate", "relu_squared", "gelu_tanh", "latent_prepare", "qkv_prepare",
+                                     "layernorm", "layernorm_pair", "token_shift", "clamped_glu", "sum_bias", "act_mul", "axpby"],
                     default="channel_gate", help="pointwise: which kernel (--tokens rows; --heads x --head-dim, or --n, columns)")
     ap.add_argument("--experts", type=int, default=14, help="experts: how many experts")
     ap.add_argument("--top", type=int, default=4, help="experts: choices per token")
@@ -134,6 +138,9 @@ def main(argv=None) -> int:
         else:
             rows = [(args.prefix, args.tokens)]  # a portion of a prompt behind `prefix` cached tokens
             pairs = args.tokens * (args.tokens + 1) / 2 + args.tokens * args.prefix
+            if args.window:
+                pairs = sum(min(p + 1, args.window) + min(args.keep_first, max(p + 1 - args.window, 0))
+                            for p in range(args.prefix, args.prefix + args.tokens))
             if args.chunk:
                 pairs = sum(p % args.chunk + 1 for p in range(args.prefix, args.prefix + args.tokens))
             flops = 4.0 * nq * d * pairs
@@ -145,12 +152,16 @@ def main(argv=None) -> int:
         o = torch.empty_like(q)
         if args.kernel == "attn_decode" and args.chunk:
             work = dict(bytes=args.batch * (args.context % args.chunk + 1) * nkv * d * 2 * 2)
-        extras = ops.AttentionExtras(torch.randn(nq, device=dev) if args.learned_sink else None, args.softcap, args.chunk)
+        if args.kernel == "attn_decode" and args.window:
+            work = dict(bytes=args.batch * (min(args.context + 1, args.window) + args.keep_first) * nkv * d * 2 * 2)
+        extras = ops.AttentionExtras(torch.randn(nq, device=dev) if args.learned_sink else None, args.softcap, args.chunk,
+                                     torch.randn(nq, device=dev) if args.distance_bias else None,
+                                     torch.rand(nq, device=dev) + 0.1 if args.distance_bias else None, args.keep_first)
 
         def calls(i, stream):
             k, v, ctx = sets[i]
             ctx.stream = stream
-            ops.attention(o, q, k, v, ctx, 0, d ** -0.5, args.chunk or None, extras=extras)
+            ops.attention(o, q, k, v, ctx, 0, d ** -0.5, args.window or args.chunk or None, extras=extras)
     elif args.kernel in ("gemm", "gate_up"):
         # gemm: x [m, k] times w [n, k]^T; gate_up: silu(x Wg^T) * (x Wu^T) with the stacked weight [2 n, k]
         ops.TC_GEMM = {"auto": "auto", "tcgen05": "1", "library": "0"}[args.gemm]
@@ -260,13 +271,39 @@ def main(argv=None) -> int:
         wn = torch.ones(d, device=dev)
         table = torch.randn(t, d, device=dev)
         qo = torch.empty(t, nq, d, **bf)
-        byts = {"channel_gate": 3 * t * width * 2, "head_gate": 2 * t * width * 2, "relu_squared": 2 * t * width * 2,
+        # the block's kernels: rows of --n channels (the model's width; the gated activation reads 2 n and writes n)
+        n = args.n
+        res, delta = torch.randn(t, n, device=dev), torch.randn(t, n, **bf)
+        lw, lb = (torch.randn(n, device=dev) for _ in range(2))
+        ln_a, ln_b = torch.empty(t, n, **bf), torch.empty(t, n, **bf)
+        gate_up, glu_bias = torch.randn(t, 2 * n, **bf), torch.randn(2 * n, device=dev)
+        slots = torch.zeros(2, n, **bf)
+        sctx = SimpleNamespace(row_of_token=row_of, cu_q=torch.tensor([0, t], **i32), q_start=torch.zeros(1, **i32),
+                               state_slot=torch.zeros(1, **i32), num_rows=1, stream=0)
+        byts = {"layernorm": t * n * 12, "layernorm_pair": t * n * 14, "token_shift": t * n * 4, "clamped_glu": t * n * 6,
+                "sum_bias": t * n * 6, "act_mul": t * n * 6, "axpby": t * n * 6,
+                "channel_gate": 3 * t * width * 2, "head_gate": 2 * t * width * 2, "relu_squared": 2 * t * width * 2,
                 "gelu_tanh": 2 * t * width * 2, "latent_prepare": 2 * t * d * 2, "qkv_prepare": 2 * 3 * t * width * 2}[args.op]
         work = dict(bytes=byts)
 
         def calls(i, stream):
             att, wide, feat = sets[i]
-            if args.op == "channel_gate":
+            if args.op == "layernorm":
+                ops.add_layernorm(ln_a, res, delta, lw, lb, 1e-5, stream=stream)
+            elif args.op == "layernorm_pair":
+                ops.add_layernorm(ln_a, res, delta, lw, lb, 1e-5, out2=ln_b, weight2=lb, bias2=lw, stream=stream)
+            elif args.op == "token_shift":
+                sctx.stream = stream
+                ops.token_shift(ln_b, ln_a, slots, lw, sctx)
+            elif args.op == "clamped_glu":
+                ops.clamped_glu(ln_a, gate_up, glu_bias, 7.0, 1.702, 1.0, stream=stream)
+            elif args.op == "act_mul":
+                ops.act_mul(ln_a, gate_up, "gelu_tanh", stream=stream)
+            elif args.op == "sum_bias":
+                ops.sum_bias(ln_a, delta, ln_b, lw, stream=stream)
+            elif args.op == "axpby":
+                ops.axpby(ln_a, delta, ln_b, 1.0, 1.0, stream=stream)
+            elif args.op == "channel_gate":
                 ops.channel_gate(feat[:, :width], att, wide[:, width:2 * width], d, 1.0, stream=stream)
             elif args.op == "head_gate":
                 ops.head_gate(feat[:, :width], att, wide[:, width:width + nq], d, 1.0, stream=stream)
