@@ -3,7 +3,8 @@
 config.json carries ``architecture``, ``width``, ``vocab``, ``norm.eps`` and ``layers``: one entry per layer with
 ``type`` (``attention``, ``attention_2`` or ``attention_3``), the mixer's sizes and constants under ``mixer`` (``heads``,
 ``kv_heads``, ``dim``, ``vdim``, ``scale``, ``mask.size``, and by type ``mask.keep_first``, ``rot.base`` / ``rot.dims``,
-``kv_from``: the layer whose keys and values this one reads), and the feed-forward under ``mlp``
+``kv_from``: an earlier layer with projections of its own whose cached keys and values this one reads, as that layer's
+cache holds them), and the feed-forward under ``mlp``
 (``{"kind": "dense", "ff": n, "limit": x}``, ``{"kind": "moe", "expert": {"ff": n}, "router": {"experts": e, "top": k},
 "shared": {"ff": n}}`` or null).
 """
@@ -81,10 +82,8 @@ class KovusunConfig:
                 if not 0 <= j < i or self.layers[j].kv_from is not None:
                     raise ValueError(f"layer {i}: kv_from={j} must name an earlier layer with keys and values of its own")
                 o = self.layers[j].mixer
-                if self.layers[j].type != layer.type or any(int(o[k]) != int(m[k]) for k in ("kv_heads", "dim", "vdim")):
-                    raise ValueError(f"layer {i} cannot read the keys and values of layer {j}: type, kv_heads, dim and vdim must agree")
-                if (o.get("rot") or None) != (m.get("rot") or None):
-                    raise ValueError(f"layer {i} cannot read the keys of layer {j}: their rotations differ")
+                if any(int(o[k]) != int(m[k]) for k in ("kv_heads", "dim", "vdim")):
+                    raise ValueError(f"layer {i} cannot read the keys and values of layer {j}: kv_heads, dim and vdim must agree")
             mlp = layer.mlp
             if mlp is not None and mlp["kind"] == "moe":
                 r = mlp["router"]

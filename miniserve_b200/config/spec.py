@@ -95,6 +95,7 @@ class ModelSpec:
     final_norm_prefix: str  # tensor-name prefix of the norm before the head (e.g. ``model.norm.``)
     checkpoint_rules: tuple[TensorRule, ...] = ()
     transitions: tuple[PartSpec, ...] = ()  # parts of category ``transition`` that run entries may name
+    optional_tensors: tuple[str, ...] = ()  # checkpoint tensors that no part declares and that may be present all the same
 
     def __post_init__(self):
         for i, e in enumerate(self.run_order):

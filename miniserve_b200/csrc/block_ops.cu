@@ -20,7 +20,7 @@
 //   * token shift: h_t + (h_(t-1) - h_t) * mix per channel, the token before a portion's first one taken from the
 //     request's state slot (zeros at position 0), and the kernel that leaves a portion's last h in the slot;
 //   * a gated activation with biases and clamps: g = min(gate + b, limit), u = clamp(up + b, -limit, limit),
-//     g * sigmoid(alpha * g) * (u + shift);
+//     g * sigmoid(alpha * g) * (u + shift) (a negative limit: no clamps);
 //   * a float32 row vector added to every row of a matrix in the run's dtype, optionally with a second matrix.
 //
 // Statistics, gates, angles and the residual sum are float32; each output is rounded once.
@@ -185,7 +185,7 @@ __global__ void shift_state_update_kernel(T* __restrict__ state, const T* __rest
 }
 
 // out[t, c] = g * sigmoid(alpha * g) * (u + shift) with g = min(gate_up[t, c] + bias[c], limit) and
-// u = clamp(gate_up[t, I + c] + bias[I + c], -limit, limit); bias [2 I] float32 or null; limit <= 0: no clamps.
+// u = clamp(gate_up[t, I + c] + bias[I + c], -limit, limit); bias [2 I] float32 or null; limit < 0: no clamps.
 template <typename T>
 __global__ void clamped_glu_kernel(T* __restrict__ out, const T* __restrict__ gate_up, const float* __restrict__ bias, int inter,
                                    long long total, float limit, float alpha, float shift) {
@@ -199,7 +199,7 @@ __global__ void clamped_glu_kernel(T* __restrict__ out, const T* __restrict__ ga
     g += bias[c];
     u += bias[inter + c];
   }
-  if (limit > 0.f) {
+  if (limit >= 0.f) {
     g = fminf(g, limit);
     u = fminf(fmaxf(u, -limit), limit);
   }
@@ -226,7 +226,7 @@ __global__ void clamped_glu_bf16x8_kernel(__nv_bfloat16* __restrict__ out, const
   }
 #pragma unroll
   for (int e = 0; e < 8; ++e) {
-    if (limit > 0.f) {
+    if (limit >= 0.f) {
       g[e] = fminf(g[e], limit);
       u[e] = fminf(fmaxf(u[e], -limit), limit);
     }

@@ -28,7 +28,7 @@ def parse_dtype(dtype: str | torch.dtype) -> torch.dtype:
 
 def _ignorable(model: DecoderModel) -> set[str]:
     head = model.head
-    return {head.name} if getattr(head, "tied", False) else set()
+    return ({head.name} if getattr(head, "tied", False) else set()) | set(model.spec.optional_tensors)
 
 
 def load_model(model_dir: str | Path, dtype: str | torch.dtype = "bfloat16",

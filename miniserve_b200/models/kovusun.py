@@ -56,7 +56,8 @@ def _feed_forward(width: int, mlp) -> PartSpec | None:
         return None
     if mlp["kind"] == "dense":
         return PartSpec("clamped_glu", dict(
-            hidden=width, intermediate=int(mlp["ff"]), limit=float(mlp["limit"]), alpha=1.702, up_shift=1.0, bias=True,
+            hidden=width, intermediate=int(mlp["ff"]), limit=float(mlp["limit"]) if mlp.get("limit") is not None else None, alpha=1.702,
+            up_shift=1.0, bias=True,
             names=dict(gate="gate", up="up", down="down", gate_bias="gate.b", up_bias="up.b", down_bias="down.b")))
     r = mlp["router"]
     shared = mlp.get("shared")
@@ -80,11 +81,13 @@ def kovusun_model_spec(cfg: KovusunConfig) -> ModelSpec:
         block = PartSpec("parallel_dual_norm", dict(names=names, token_shift="shift", hidden=cfg.width))
         layers.append(LayerSpec(prefix=f"l{i}.", block=block, mixer=_mixer(cfg, i, layer), feed_forward=ffn, norms=norms))
     run_order = tuple(RunEntry(i, cache_of=layer.kv_from) for i, layer in enumerate(cfg.layers))
+    # a layer without a feed-forward has nothing for a second norm to feed: a checkpoint may carry its tensors all the same
+    spare = tuple(f"l{i}.norm2{suffix}" for i, layer in enumerate(cfg.layers) if layer.mlp is None for suffix in ("", ".b"))
     return ModelSpec(
         architecture="Kovusun", hidden_size=cfg.width, vocab_size=cfg.vocab,
         embedding=PartSpec("token_embedding", dict(vocab=cfg.vocab, hidden=cfg.width, name="embed")),
         layers=tuple(layers), run_order=run_order, final_norm=norm, final_norm_prefix="final.norm",
-        head=PartSpec("linear_head", dict(vocab=cfg.vocab, hidden=cfg.width, tied=False, name="head")))
+        head=PartSpec("linear_head", dict(vocab=cfg.vocab, hidden=cfg.width, tied=False, name="head")), optional_tensors=spare)
 
 
 KOVUSUN = register_architecture(Architecture("Kovusun", KovusunConfig.from_dict, kovusun_model_spec), replace=True)

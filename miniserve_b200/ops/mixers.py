@@ -159,7 +159,7 @@ def shift_state_update(state, h, ctx) -> None:
 
 def clamped_glu(out, gate_up, bias, limit: float, alpha: float, shift: float, stream=None) -> None:
     """out[t, c] = g * sigmoid(alpha * g) * (u + shift), g = min(gate_up[t, c] + bias[c], limit), u = clamp(gate_up[t, I + c] +
-    bias[I + c], -limit, limit); ``bias`` float32 [2 I] or None; ``limit`` 0: no clamps. float32 arithmetic, one rounding."""
+    bias[I + c], -limit, limit); ``bias`` float32 [2 I] or None; a negative ``limit``: no clamps. float32 arithmetic, one rounding."""
     t, inter = out.shape
     _f32(bias)
     assert gate_up.shape == (t, 2 * inter) and gate_up.dtype == out.dtype and out.is_contiguous() and gate_up.is_contiguous()

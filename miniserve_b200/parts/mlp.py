@@ -69,7 +69,7 @@ class ClampedGLU(Part):
     """down(g * sigmoid(alpha g) * (u + up_shift)) with g = min(gate(x), limit) and u = clamp(up(x), -limit, limit); every
     projection may have a bias. The gate and up matrices are stacked as in ``swiglu``; their biases are added, and the
     clamps and the activation computed, in float32 by one kernel behind the product. Parameters: ``hidden``,
-    ``intermediate``, ``limit`` (0: no clamps), optional ``alpha`` (1.702), ``up_shift`` (1.0), ``bias`` (True), ``names``
+    ``intermediate``, ``limit`` (absent: no clamps), optional ``alpha`` (1.702), ``up_shift`` (1.0), ``bias`` (True), ``names``
     (gate / up / down and gate_bias / up_bias / down_bias -> tensor names)."""
     shape_static = True
     NAMES = dict(gate="gate_proj.weight", up="up_proj.weight", down="down_proj.weight", gate_bias="gate_proj.bias",
@@ -79,11 +79,11 @@ class ClampedGLU(Part):
         super().__init__(spec, env)
         self.hidden = param(spec, "hidden", int)
         self.inter = param(spec, "intermediate", int)
-        self.limit = float(spec.get("limit") or 0.0)
+        self.limit = float(spec["limit"]) if spec.get("limit") is not None else -1.0  # negative: no clamps
         self.alpha = float(spec.get("alpha", 1.702))
         self.up_shift = float(spec.get("up_shift", 1.0))
         self.bias = bool(spec.params.get("bias", True))
-        if self.limit < 0:
+        if spec.get("limit") is not None and self.limit < 0:
             raise ValueError(f"clamped_glu: limit={self.limit} must not be negative")
         self.names = {**self.NAMES, **dict(spec.get("names") or {})}
 

@@ -51,6 +51,14 @@ def test_run_order_caches_and_shared_keys():
     assert model.layers[2].mixer.reach == 21 and model.layers[0].mixer.reach == 13
 
 
+def test_a_reader_may_read_a_layer_of_another_kind_and_a_spare_norm_is_tolerated():
+    raw = kx.config([kx.sink_layer(heads=4, kv_heads=2, dim=16, vdim=16, window=12), kx.biased_layer(window=20, kv_from=0)])
+    _, _, spec = resolve(raw)
+    model = DecoderModel(spec, torch.float32, "cpu")
+    assert model.entry_caches[1].shares == 0 and model.entry_caches[0].need[1] == PagedKV(2, 16, 20)
+    assert set(spec.optional_tensors) == {"l0.norm2", "l0.norm2.b", "l1.norm2", "l1.norm2.b"}  # neither layer has a feed-forward
+
+
 def test_a_reader_of_keys_with_kept_first_keys_keeps_every_page():
     own = kx.rotary_layer(window=9, keep_first=0)
     reader = kx.rotary_layer(window=30, keep_first=4)
@@ -62,7 +70,7 @@ def test_a_reader_of_keys_with_kept_first_keys_keeps_every_page():
 
 @pytest.mark.parametrize("change, error", [
     (lambda raw: raw["layers"][2]["mixer"].update(kv_from=2), ValueError),
-    (lambda raw: raw["layers"][2]["mixer"].update(kv_from=1), ValueError),  # another type of mixer
+    (lambda raw: raw["layers"][2]["mixer"].update(kv_from=1), ValueError),  # a layer of other key and value sizes
     (lambda raw: raw["layers"][2]["mixer"].update(dim=32), ValueError),  # other sizes than the owner's
     (lambda raw: raw["layers"][0].update(type="attention_9"), NotImplementedError),
     (lambda raw: raw["layers"][0]["mlp"].update(kind="sparse"), NotImplementedError),

@@ -343,6 +343,26 @@ def test_a_reader_of_another_layers_keys_and_values(dtype):
     _close(torch.cat(outs_r), ref_reader, dtype, 3.0)
 
 
+@pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
+def test_a_reader_of_a_layer_of_another_kind_and_a_zero_limit(dtype, tmp_path):
+    """A layer with biases and a distance bias reads the keys and values of a layer with a sink and a gate (unit-normed
+    keys without biases, as that layer's cache holds them); the checkpoint carries a second norm for a layer without a
+    feed-forward; a dense feed-forward with a limit of zero (the gate never above zero, up always zero)."""
+    raw = kx.config([kx.sink_layer(heads=4, kv_heads=2, dim=16, vdim=16, window=12, mlp=kx.dense(40, limit=0.0)),
+                     kx.biased_layer(heads=6, kv_heads=2, dim=16, vdim=16, window=20, kv_from=0)], width=40, vocab=53)
+
+    def spare(w):
+        w["l1.norm2"] = torch.ones(40, dtype=torch.bfloat16)
+        w["l1.norm2.b"] = torch.zeros(40, dtype=torch.bfloat16)
+    folder = kx.write_model(tmp_path / "m", raw, seed=31, change=spare)
+    ids = _ids(70, 53, 6)
+    run = kx.Runner(folder, dtype, max_tokens=128, page_size=8)
+    model = dict(oracle=kx.oracle(folder), rounded=kx.oracle(folder, torch.bfloat16))
+    _logits_close(model, dtype, run.feed("w", ids, [70]), ids, "whole")
+    _logits_close(model, dtype, run.feed("c", ids, [9, 2, 30, 1, 1, 1, 5, 2]), ids, "in portions")
+    assert run.cache.is_idle()
+
+
 @pytest.mark.parametrize("dtype", DTYPES)
 def test_sink_takes_its_share_and_the_gate_closes_heads(dtype):
     att, m = _mixer(dtype, "attention_2", heads=2, kv_heads=1, dim=16, vdim=16, window=30, scale=0.3)
