@@ -86,7 +86,7 @@ def config_c():
         own,
         rotary_layer(heads=4, kv_heads=2, dim=128, vdim=128, window=40, keep_first=16, rot=64, base=50000.0, scale=0.09, mlp=dense(320, limit=2.0)),
         biased_layer(heads=8, kv_heads=4, dim=32, vdim=32, window=96, scale=0.18, kv_from=0, mlp=dense(192, limit=1.0)),
-        sink_layer(heads=4, kv_heads=2, dim=64, vdim=48, window=72, scale=0.125, mlp=moe(ff=64, experts=8, top=2, shared=96)),
+        sink_layer(heads=4, kv_heads=4, dim=64, vdim=32, window=80, scale=0.11, mlp=moe(ff=64, experts=8, top=2, shared=96)),
         biased_layer(heads=8, kv_heads=4, dim=32, vdim=32, window=24, scale=0.18, kv_from=0, mlp=None),
     ], width=256, vocab=640)
 
