@@ -422,7 +422,7 @@ def qkv_norm_rope_kv(q_out: torch.Tensor, k_pool: torch.Tensor, v_pool: torch.Te
     nkv = k_pool.shape[1]
     assert d == 128 and k_pool.shape == v_pool.shape and k_pool.shape[2] == page_size and k_pool.shape[3] == d
     assert x.dtype == torch.bfloat16 and w_qkv.shape == ((nq + 2 * nkv) * d, x.shape[1]) and x.shape[0] == t
-    assert cos_sin is None or (cos_sin.dtype == torch.float32 and cos_sin.shape == (-(-t // 128), 8, 2, 128, 8))
+    assert cos_sin is None or (cos_sin.dtype == torch.float32 and cos_sin.shape == (2 * -(-t // 256), 8, 2, 128, 8))
     lib = native.gemm_tc()
     native.kernel_check(lib.ms_gemm_tc_qkv_bf16(
         _ptr(q_out), _ptr(x), _ptr(w_qkv), t, x.shape[1], nq, nkv, _ptr(k_pool), _ptr(v_pool), _ptr(q_norm_w), _ptr(k_norm_w),
@@ -441,12 +441,13 @@ def rope_table(positions: torch.Tensor, inv_freq: torch.Tensor, num_tokens: int,
 
 def rope_table_tiled(table: torch.Tensor, stream=None) -> torch.Tensor:
     """The cos/sin table [T, 128] of a step laid out by tiles of 128 tokens and eighths of the 64 rotation
-    pairs, float32 [ceil(T / 128), 8, 2, 128, 8]: what ``qkv_norm_rope_kv`` reads (a piece per bulk copy).
-    Rows of the last tile beyond T are not written."""
+    pairs, float32 [tiles, 8, 2, 128, 8]: what ``qkv_norm_rope_kv`` reads (a piece per bulk copy). The tiles come in
+    pairs, 2 * ceil(T / 256) of them: the product's pair of CTAs covers 256 rows and each of the two fetches the pieces
+    of its 128 rows whether the step has that many tokens or not. Rows beyond T are not written (nor used)."""
     _check_dev(table)
     assert table.dtype == torch.float32 and table.dim() == 2 and table.shape[1] == 128
     t = table.shape[0]
-    tiled = torch.empty((-(-t // 128), 8, 2, 128, 8), dtype=torch.float32, device=table.device)
+    tiled = torch.empty((2 * -(-t // 256), 8, 2, 128, 8), dtype=torch.float32, device=table.device)
     k = native.kernels()
     native.kernel_check(k.ms_rope_table_tile(_ptr(tiled), _ptr(table), t, _stream(stream)))
     return tiled
