@@ -690,8 +690,12 @@ attn_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_c
                                                 EXTRAS ? gr.keep - key0 : 0, dist_c, dist_r2, qpos - key0);
           }
           l_sum += (part[0] + part[1]) + (part[2] + part[3]);
+          // Rows of V that no query may weigh: keys beyond the request's end, and keys that the window of every row of
+          // this item has passed and that are not kept first keys. Their pages may have been given back and hold
+          // anything (a probability of zero times a NaN is a NaN), so they are made zero.
           const int valid_keys = kv_len - key0;
-          if (valid_keys < AT_KEYS && row >= valid_keys) {
+          const bool passed = key0 + row < it.lo_g[0] && key0 + row >= gr.keep;
+          if ((valid_keys < AT_KEYS && row >= valid_keys) || passed) {
             unsigned char* vt = smem + AtSmem::kv + (j & 1) * AtSmem::stage + 2 * AT_BLOCK;
   #pragma unroll
             for (int h = 0; h < 2; ++h)

@@ -363,6 +363,22 @@ def test_a_reader_of_a_layer_of_another_kind_and_a_zero_limit(dtype, tmp_path):
     assert run.cache.is_idle()
 
 
+@pytest.mark.parametrize("seed", [5, 6, 7])
+def test_pages_given_back_behind_a_window_are_not_weighed(seed, tmp_path):
+    """Values of 128 channels under a window of 33: prompts' portions run on the tcgen05 kernel, whose first key tile
+    reaches back over pages that the window has given back (NaN-filled here). A probability of zero times a NaN is a
+    NaN, so those rows of V must not reach the product."""
+    raw = kx.config([kx.biased_layer(heads=2, kv_heads=1, dim=32, vdim=128, window=33, mlp=kx.dense(48)),
+                     kx.sink_layer(heads=2, kv_heads=2, dim=128, vdim=64, window=20, scale=0.09)], width=64, vocab=71)
+    folder = kx.write_model(tmp_path / "m", raw, seed=seed)
+    ids = _ids(230, 71, seed)
+    run = kx.Runner(folder, "bfloat16", max_tokens=256, page_size=16)
+    got = run.feed("c", ids, [64, 2, 37, 1, 1, 1, 50, 3, 1, 1, 40, 2])
+    assert not torch.isnan(got).any(), f"NaN from position {int(torch.isnan(got).any(dim=1).nonzero()[0])} on"
+    ok, report = kx.rounded_ok(got, kx.oracle(folder)(ids), kx.oracle(folder, torch.bfloat16)(ids))
+    assert ok, report
+
+
 @pytest.mark.parametrize("dtype", DTYPES)
 def test_sink_takes_its_share_and_the_gate_closes_heads(dtype):
     att, m = _mixer(dtype, "attention_2", heads=2, kv_heads=1, dim=16, vdim=16, window=30, scale=0.3)
